@@ -1,0 +1,237 @@
+// C ABI of libfta (declared in include/fta.h): argument validation, TMA tensor maps, launches.
+// Nothing here allocates device memory; every buffer belongs to the caller.
+#include "../../include/fta.h"
+
+#include "fta_kernels.h"
+#include "tmap.h"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return FTA_ERR_CUDA;
+}
+
+int check_problem(const FtaProblem* p) {
+  if (!p) return FTA_ERR_NULL;
+  if (p->B <= 0 || p->H <= 0 || p->L1 <= 0 || p->L2 <= 0) return FTA_ERR_SHAPE;
+  if (p->L2 % 128 != 0) return FTA_ERR_SHAPE;
+  if (p->D != 32 && p->D != 64) return FTA_ERR_HEAD_DIM;
+  if (p->dtype != FTA_FP16 && p->dtype != FTA_BF16) return FTA_ERR_DTYPE;
+  if (static_cast<long long>(p->B) * p->H > 65535) return FTA_ERR_TOO_LARGE;
+  return FTA_OK;
+}
+
+int check_t5(const FtaTensor5* t) {
+  if (!t || !t->ptr) return FTA_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(t->ptr) % 16 != 0) return FTA_ERR_ALIGN;
+  if (t->stride[4] != 1) return FTA_ERR_STRIDE;
+  for (int i = 0; i < 4; ++i)
+    if (t->stride[i] <= 0 || t->stride[i] % 8 != 0) return FTA_ERR_STRIDE;
+  return FTA_OK;
+}
+
+int check_t4(const FtaTensor4* t) {
+  if (!t || !t->ptr) return FTA_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(t->ptr) % 16 != 0) return FTA_ERR_ALIGN;
+  if (t->stride[3] != 1) return FTA_ERR_STRIDE;
+  for (int i = 0; i < 3; ++i)
+    if (t->stride[i] <= 0 || t->stride[i] % 8 != 0) return FTA_ERR_STRIDE;
+  return FTA_OK;
+}
+
+// 5-D map over (D, L2, L1, H, B), tile = 128 rows of L2 x D, swizzle = row bytes (64 or 128).
+int map5(CUtensorMap* m, const FtaProblem* p, const FtaTensor5* t) {
+  const uint64_t dims[5] = {static_cast<uint64_t>(p->D), static_cast<uint64_t>(p->L2),
+                            static_cast<uint64_t>(p->L1), static_cast<uint64_t>(p->H),
+                            static_cast<uint64_t>(p->B)};
+  const uint64_t str[5] = {0, static_cast<uint64_t>(t->stride[3]) * 2, static_cast<uint64_t>(t->stride[2]) * 2,
+                           static_cast<uint64_t>(t->stride[1]) * 2, static_cast<uint64_t>(t->stride[0]) * 2};
+  const uint32_t box[5] = {static_cast<uint32_t>(p->D), 128, 1, 1, 1};
+  return fta::make_tmap_16bit(m, t->ptr, 5, dims, str, box, p->D * 2) == 0 ? FTA_OK : FTA_ERR_TENSOR_MAP;
+}
+
+// 4-D map over the bias (key, query, H, B); `box_k` keys x 128 queries per tile.
+int map_bias(CUtensorMap* m, const FtaProblem* p, const FtaTensor4* t, int box_k, int swizzle) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(p->L2), static_cast<uint64_t>(p->L2),
+                            static_cast<uint64_t>(p->H), static_cast<uint64_t>(p->B)};
+  const uint64_t str[4] = {0, static_cast<uint64_t>(t->stride[2]) * 2, static_cast<uint64_t>(t->stride[1]) * 2,
+                           static_cast<uint64_t>(t->stride[0]) * 2};
+  const uint32_t box[4] = {static_cast<uint32_t>(box_k), 128, 1, 1};
+  return fta::make_tmap_16bit(m, t->ptr, 4, dims, str, box, swizzle) == 0 ? FTA_OK : FTA_ERR_TENSOR_MAP;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+int num_sms() {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fta_version(void) { return 100; }
+
+const char* fta_strerror(int code) {
+  switch (code) {
+    case FTA_OK: return "ok";
+    case FTA_ERR_NULL: return "a required pointer is NULL";
+    case FTA_ERR_SHAPE: return "bad shape: sizes must be positive and L2 a multiple of 128";
+    case FTA_ERR_HEAD_DIM: return "unsupported head dimension: D must be 32 or 64";
+    case FTA_ERR_DTYPE: return "unsupported dtype: fp16 or bf16 only";
+    case FTA_ERR_STRIDE: return "bad stride: D stride must be 1, other strides positive multiples of 8 elements";
+    case FTA_ERR_ALIGN: return "base pointer must be 16-byte aligned";
+    case FTA_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case FTA_ERR_TENSOR_MAP: return "the driver refused a TMA tensor map";
+    case FTA_ERR_CUDA: return "a CUDA runtime call failed";
+    case FTA_ERR_DEVICE: return "a bounded device-side wait ran out (status word non-zero)";
+    case FTA_ERR_TOO_LARGE: return "size beyond a documented maximum";
+    default: return "unknown error";
+  }
+}
+
+int fta_last_cuda_error(void) { return g_last_cuda_error; }
+
+int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k, const FtaTensor5* v,
+                const FtaTensor4* bias, float sm_scale, const FtaTensor5* o, float* lse, int32_t* status,
+                void* stream) {
+  int rc = check_problem(prob);
+  if (rc) return rc;
+  if ((rc = check_t5(q)) || (rc = check_t5(k)) || (rc = check_t5(v)) || (rc = check_t5(o)) ||
+      (rc = check_t4(bias)))
+    return rc;
+  if (!lse || !status) return FTA_ERR_NULL;
+  fta::FwdArgs a;
+  if ((rc = map5(&a.tmQ, prob, q)) || (rc = map5(&a.tmK, prob, k)) || (rc = map5(&a.tmV, prob, v)) ||
+      (rc = map_bias(&a.tmBias, prob, bias, 64, 128)))
+    return rc;
+  a.o = o->ptr;
+  a.lse = lse;
+  a.status = status;
+  a.B = prob->B;
+  a.H = prob->H;
+  a.L1 = prob->L1;
+  a.L2 = prob->L2;
+  a.D = prob->D;
+  a.bf16 = prob->dtype == FTA_BF16;
+  for (int i = 0; i < 4; ++i) a.so[i] = o->stride[i];
+  a.sm_scale = sm_scale;
+  if (fta::launch_fwd(a, static_cast<cudaStream_t>(stream)) != 0) return cuda_fail(cudaGetLastError());
+  return FTA_OK;
+}
+
+int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const FtaTensor5* dout, float* delta,
+                       void* stream) {
+  int rc = check_problem(prob);
+  if (rc) return rc;
+  if ((rc = check_t5(o)) || (rc = check_t5(dout))) return rc;
+  if (!delta) return FTA_ERR_NULL;
+  long long so[4], sd[4];
+  for (int i = 0; i < 4; ++i) {
+    so[i] = o->stride[i];
+    sd[i] = dout->stride[i];
+  }
+  if (fta::launch_preprocess(o->ptr, so, dout->ptr, sd, delta, prob->B, prob->H, prob->L1, prob->L2, prob->D,
+                             prob->dtype == FTA_BF16, static_cast<cudaStream_t>(stream)) != 0)
+    return cuda_fail(cudaGetLastError());
+  return FTA_OK;
+}
+
+int fta_bwd_num_planes(const FtaProblem* prob) {
+  if (check_problem(prob)) return 0;
+  return fta::bwd_num_planes(prob->B, prob->H, prob->L1, prob->L2, prob->D, num_sms());
+}
+
+size_t fta_bwd_workspace_bytes(const FtaProblem* prob) {
+  if (check_problem(prob)) return 0;
+  const size_t rows = static_cast<size_t>(prob->B) * prob->H * prob->L1 * prob->L2;
+  const size_t plane = static_cast<size_t>(prob->B) * prob->H * prob->L2 * prob->L2 * sizeof(float);
+  return align256(rows * prob->D * sizeof(float)) + align256(plane * fta_bwd_num_planes(prob));
+}
+
+int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k, const FtaTensor5* v,
+                 const FtaTensor4* bias, const FtaTensor5* dout, const float* lse, const float* delta,
+                 float sm_scale, const FtaTensor5* dq, const FtaTensor5* dk, const FtaTensor5* dv,
+                 float* dbias_f32, void* dbias_cast, void* workspace, size_t workspace_bytes, int32_t* status,
+                 void* stream) {
+  int rc = check_problem(prob);
+  if (rc) return rc;
+  if ((rc = check_t5(q)) || (rc = check_t5(k)) || (rc = check_t5(v)) || (rc = check_t5(dout)) ||
+      (rc = check_t5(dq)) || (rc = check_t5(dk)) || (rc = check_t5(dv)) || (rc = check_t4(bias)))
+    return rc;
+  if (!lse || !delta || !dbias_f32 || !status || !workspace) return FTA_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < fta_bwd_workspace_bytes(prob))
+    return FTA_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t rows = static_cast<size_t>(prob->B) * prob->H * prob->L1 * prob->L2;
+  const size_t dq_bytes = rows * prob->D * sizeof(float);
+  const long long plane_elems = static_cast<long long>(prob->B) * prob->H * prob->L2 * prob->L2;
+  float* dq32 = static_cast<float*>(workspace);
+  float* planes = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + align256(dq_bytes));
+  const bool bf16 = prob->dtype == FTA_BF16;
+
+  fta::BwdArgs a;
+  if ((rc = map5(&a.tmQ, prob, q)) || (rc = map5(&a.tmK, prob, k)) || (rc = map5(&a.tmV, prob, v)) ||
+      (rc = map5(&a.tmDO, prob, dout)) || (rc = map_bias(&a.tmBias, prob, bias, 128, 0)))
+    return rc;
+  a.lse = lse;
+  a.delta = delta;
+  a.dq32 = dq32;
+  a.dk = dk->ptr;
+  a.dv = dv->ptr;
+  a.planes = planes;
+  a.status = status;
+  a.B = prob->B;
+  a.H = prob->H;
+  a.L1 = prob->L1;
+  a.L2 = prob->L2;
+  a.D = prob->D;
+  a.bf16 = bf16;
+  long long sdq[4];
+  for (int i = 0; i < 4; ++i) {
+    a.sdk[i] = dk->stride[i];
+    a.sdv[i] = dv->stride[i];
+    sdq[i] = dq->stride[i];
+  }
+  a.sm_scale = sm_scale;
+
+  cudaError_t e = cudaMemsetAsync(dq32, 0, dq_bytes, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (fta::launch_bwd(a, st) != 0) return cuda_fail(cudaGetLastError());
+  if (fta::launch_dq_finalize(dq32, dq->ptr, sdq, prob->B, prob->H, prob->L1, prob->L2, prob->D, sm_scale, bf16,
+                              st) != 0)
+    return cuda_fail(cudaGetLastError());
+  if (fta::launch_dbias_finalize(planes, fta_bwd_num_planes(prob), plane_elems, dbias_f32, dbias_cast, bf16,
+                                 st) != 0)
+    return cuda_fail(cudaGetLastError());
+  return FTA_OK;
+}
+
+int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* stream) {
+  if (!src || !dst) return FTA_ERR_NULL;
+  if (n <= 0 || n % 4 != 0) return FTA_ERR_SHAPE;
+  if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
+  if (fta::launch_dbias_finalize(src, 1, n, nullptr, dst, dtype == FTA_BF16, static_cast<cudaStream_t>(stream)) !=
+      0)
+    return cuda_fail(cudaGetLastError());
+  return FTA_OK;
+}
+
+int fta_read_status(const int32_t* status, int32_t* code_out, void* stream) {
+  if (!status) return FTA_ERR_NULL;
+  int32_t host = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (code_out) *code_out = host;
+  return host == 0 ? FTA_OK : FTA_ERR_DEVICE;
+}
+
+}  // extern "C"

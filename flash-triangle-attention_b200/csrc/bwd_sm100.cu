@@ -1,0 +1,523 @@
+// Backward triangle attention for sm_100a: dQ, dK, dV and dBias, the work of the reference's
+// `_attn_bwd` (flash_tt_attn.py:442-550) with each score tile visited ONCE (5 MMAs and one
+// exp2 per score instead of the reference's two passes).
+//
+// A CTA owns one key block `kb` of one (b,h) and a fixed residue class `r` of the groups of
+// G consecutive L1 rows (groups r, r+NP, r+2NP, ...). For each group it keeps K/V of the G
+// rows in shared memory and dK/dV of the G rows in TMEM, and walks the query blocks `jb`
+// (outer) and the G rows (inner):
+//
+//   S^T  = K Q^T, dP^T = V dO^T                       (tcgen05, operands in smem)
+//   P^T  = exp2(S^T*c1 + bias^T*log2e - lse),  dS^T = P^T * (dP^T - delta)   (CUDA cores)
+//   dV  += P^T dO, dK += dS^T Q                        (A operand read from TMEM)
+//   dQ   = dS K                                        (dS staged in smem, M-major)
+//
+// The tile is split in two 64-query halves, one per compute warpgroup, each with its own
+// S^T / dP^T columns and barriers, so the tensor core works on one half while the CUDA cores
+// work on the other.
+//
+// dBias: each thread owns one key column and 64 query rows of the (jb,kb) tile and sums dS
+// (float32, before rounding) over the G rows in registers; the sums are then added to the
+// CTA's PRIVATE float32 plane (plane index r) with `red.global.add.f32`. A plane element is
+// only ever touched by one thread of one CTA, in program order, so the result is bit-exact
+// run to run; the planes are summed in fixed order by the finalise kernel.
+// dQ leaves the CTA as float32 reductions into a zero-initialised buffer (sum over key blocks).
+//
+//   warps 0-3 : compute warpgroup 0 (queries 0..63 of the tile)   also stores dV
+//   warps 4-7 : compute warpgroup 1 (queries 64..127)             also reduces dQ, stores dK
+//   warp 8    : TMA producer      warp 9 : tcgen05 issuer      warps 10-11 : idle
+#include "fta_kernels.h"
+#include "tc05.cuh"
+
+namespace fta {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int kD>
+struct BwdCfg {
+  static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + D + 2*D*G <= 512)
+  static constexpr int NQ = 2;                  // Q/dO ring depth
+  static constexpr int TILE_B = 128 * kD * 2;
+  static constexpr int STAGE_B = 2 * TILE_B + 1024;  // Q, dO, lse[128], delta[128]
+  static constexpr int BIAS_B = 128 * 128 * 2;
+  static constexpr int DS_B = 128 * 128 * 2;
+  static constexpr int OFF_KV = 0;
+  static constexpr int OFF_QDO = OFF_KV + G * 2 * TILE_B;
+  static constexpr int OFF_BIAS = OFF_QDO + NQ * STAGE_B;
+  static constexpr int OFF_DS = OFF_BIAS + 2 * BIAS_B;
+  static constexpr int OFF_BAR = OFF_DS + DS_B;
+  static constexpr int B_KVFULL = 0;
+  static constexpr int B_KVFREE = 1;
+  static constexpr int B_QDOFULL = 2;
+  static constexpr int B_QDOEMPTY = B_QDOFULL + NQ;
+  static constexpr int B_BIASFULL = B_QDOEMPTY + NQ;
+  static constexpr int B_BIASEMPTY = B_BIASFULL + 2;
+  static constexpr int B_SFULL = B_BIASEMPTY + 2;
+  static constexpr int B_PFULL = B_SFULL + 2;
+  static constexpr int B_DQDONE = B_PFULL + 2;
+  static constexpr int B_ACCFULL = B_DQDONE + 1;
+  static constexpr int B_ACCFREE = B_ACCFULL + 1;
+  static constexpr int NBAR = B_ACCFREE + 1;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
+  static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
+  static constexpr uint32_t ROW_B = kD * 2;
+  static constexpr uint32_t SBO = 8 * ROW_B;
+  // TMEM columns
+  static constexpr uint32_t TM_ST = 0;
+  static constexpr uint32_t TM_DP = 128;
+  static constexpr uint32_t TM_DQ = 256;
+  static constexpr uint32_t TM_ACC = 256 + kD;  // dK_g at TM_ACC + g*2*kD, dV_g right after
+  static_assert(TM_ACC + G * 2 * kD <= 512, "TMEM budget");
+};
+
+struct BwdParams {
+  const float* lse;
+  const float* delta;
+  float* dq32;
+  void* dk;
+  void* dv;
+  float* planes;
+  int* status;
+  int H, L1, L2, NP, BH;
+  long long sdk[4], sdv[4];
+  float c1;     // sm_scale * log2(e)
+  float scale;  // sm_scale
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void red_add(float* addr, float a) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
+}
+
+template <bool kBf16>
+__device__ __forceinline__ float ld16_as_float(const uint8_t* p) {
+  const uint16_t v = *reinterpret_cast<const uint16_t*>(p);
+  if constexpr (kBf16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  else return __half2float(__ushort_as_half(v));
+}
+
+template <int kD, bool kBf16>
+__global__ void __launch_bounds__(384, 1)
+fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+               const __grid_constant__ CUtensorMap tmBias, const BwdParams p) {
+  using C = BwdCfg<kD>;
+  constexpr int G = C::G;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sKV = smem + C::OFF_KV;    // [g][K tile | V tile]
+  uint8_t* sQDO = smem + C::OFF_QDO;  // [stage][Q | dO | lse | delta]
+  uint8_t* sBias = smem + C::OFF_BIAS;
+  uint8_t* sDS = smem + C::OFF_DS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = p.L2 / 128, nq = p.L2 / 128;
+  const int kb = blockIdx.x % nkb;
+  const int r = (blockIdx.x / nkb) % p.NP;
+  const int bh = blockIdx.x / (nkb * p.NP);
+  const int b = bh / p.H, h = bh % p.H;
+  const int ngroups_total = (p.L1 + G - 1) / G;
+  const int ngroups = (ngroups_total - r + p.NP - 1) / p.NP;  // groups r, r+NP, ...
+  const WaitCtx w{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar(C::B_KVFULL), 1);
+    mbar_init(bar(C::B_KVFREE), 1);
+    for (int i = 0; i < C::NQ; ++i) {
+      mbar_init(bar(C::B_QDOFULL + i), 1);
+      mbar_init(bar(C::B_QDOEMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(C::B_BIASFULL + i), 1);
+      mbar_init(bar(C::B_BIASEMPTY + i), 8);
+      mbar_init(bar(C::B_SFULL + i), 1);
+      mbar_init(bar(C::B_PFULL + i), 128);
+    }
+    mbar_init(bar(C::B_DQDONE), 1);
+    mbar_init(bar(C::B_ACCFULL), 1);
+    mbar_init(bar(C::B_ACCFREE), 256);
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = *tmem_slot;
+
+  if (warp >= 8) reg_dec<88>();
+  else reg_inc<208>();
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      tma_prefetch_desc(&tmBias);
+      bool ok = true;
+      int tt = 0, nb = 0;
+      for (int n = 0; n < ngroups && ok; ++n) {
+        const int i0 = (r + n * p.NP) * G;
+        const int Gc = min(G, p.L1 - i0);
+        ok = mbar_wait(bar(C::B_KVFREE), (n & 1) ^ 1, w, 0x21);
+        if (!ok) break;
+        mbar_expect_tx(bar(C::B_KVFULL), Gc * 2 * C::TILE_B);
+        for (int g = 0; g < Gc; ++g) {
+          tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL), 0, kb * 128, i0 + g, h, b);
+          tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL), 0, kb * 128,
+                      i0 + g, h, b);
+        }
+        for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
+          const int bs = nb & 1;
+          ok = mbar_wait(bar(C::B_BIASEMPTY + bs), ((nb >> 1) & 1) ^ 1, w, 0x22);
+          if (!ok) break;
+          mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
+          tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128, jb * 128,
+                      h, b);
+          for (int g = 0; g < Gc; ++g, ++tt) {
+            const int s = tt % C::NQ;
+            ok = mbar_wait(bar(C::B_QDOEMPTY + s), ((tt / C::NQ) & 1) ^ 1, w, 0x23);
+            if (!ok) break;
+            uint8_t* st = sQDO + s * C::STAGE_B;
+            mbar_expect_tx(bar(C::B_QDOFULL + s), C::STAGE_B);
+            tma_load_5d(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
+            tma_load_5d(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
+            const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
+            bulk_load_1d(smem_u32(st + 2 * C::TILE_B), p.lse + roff, 512, bar(C::B_QDOFULL + s));
+            bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.delta + roff, 512, bar(C::B_QDOFULL + s));
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr int fmt = kBf16 ? 1 : 0;
+      constexpr uint32_t idesc_s = umma_idesc_f16(fmt, 128, 64, 0, 0);    // S^T, dP^T halves
+      constexpr uint32_t idesc_acc = umma_idesc_f16(fmt, 128, kD, 0, 1);  // dV, dK (A in TMEM, B M-major)
+      constexpr uint32_t idesc_dq = umma_idesc_f16(fmt, 128, kD, 1, 1);   // dQ (A, B M-major)
+      bool ok = true;
+      int tt = 0;
+      // S^T_w / dP^T_w of the tile with ring index `tix`, row g of the group
+      auto issue_sdp = [&](int tix, int g, int wh, bool wait_stage) -> bool {
+        const int s = tix % C::NQ;
+        if (wait_stage && !mbar_wait(bar(C::B_QDOFULL + s), (tix / C::NQ) & 1, w, 0x31)) return false;
+        tc_fence_after_sync();
+        const uint8_t* st = sQDO + s * C::STAGE_B;
+        const uint64_t dK = umma_smem_desc(smem_u32(sKV + g * 2 * C::TILE_B), 16, C::SBO, C::SWZ);
+        const uint64_t dV = umma_smem_desc(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), 16, C::SBO, C::SWZ);
+        const uint64_t dQ = umma_smem_desc(smem_u32(st + wh * 64 * C::ROW_B), 16, C::SBO, C::SWZ);
+        const uint64_t dO = umma_smem_desc(smem_u32(st + C::TILE_B + wh * 64 * C::ROW_B), 16, C::SBO, C::SWZ);
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks)
+          umma_ss(tbase + C::TM_ST + wh * 64, dK + ks * 2, dQ + ks * 2, idesc_s, ks > 0);
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks)
+          umma_ss(tbase + C::TM_DP + wh * 64, dV + ks * 2, dO + ks * 2, idesc_s, ks > 0);
+        umma_commit(bar(C::B_SFULL + wh));
+        return true;
+      };
+      for (int n = 0; n < ngroups && ok; ++n) {
+        const int i0 = (r + n * p.NP) * G;
+        const int Gc = min(G, p.L1 - i0);
+        const int T = nq * Gc;
+        ok = mbar_wait(bar(C::B_KVFULL), n & 1, w, 0x32);
+        if (!ok) break;
+        ok = issue_sdp(tt, 0, 0, true) && issue_sdp(tt, 0, 1, false);
+        for (int t = 0; t < T && ok; ++t, ++tt) {
+          const int jb = t / Gc, g = t % Gc, s = tt % C::NQ;
+          const uint8_t* st = sQDO + s * C::STAGE_B;
+          for (int wh = 0; wh < 2 && ok; ++wh) {
+            ok = mbar_wait(bar(C::B_PFULL + wh), tt & 1, w, 0x33);
+            if (!ok) break;
+            if (t == 0 && wh == 0 && n > 0) {
+              ok = mbar_wait(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
+              if (!ok) break;
+            }
+            tc_fence_after_sync();
+            const uint64_t dOm =
+                umma_smem_desc(smem_u32(st + C::TILE_B + wh * 64 * C::ROW_B), C::SBO, C::SBO, C::SWZ);
+            const uint64_t dQm = umma_smem_desc(smem_u32(st + wh * 64 * C::ROW_B), C::SBO, C::SBO, C::SWZ);
+            const uint32_t tdk = tbase + C::TM_ACC + g * 2 * kD, tdv = tdk + kD;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ts(tdv, tbase + C::TM_ST + wh * 64 + ks * 8, dOm + ks * ((2 * C::SBO) >> 4), idesc_acc,
+                      (jb > 0 || wh > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_ts(tdk, tbase + C::TM_DP + wh * 64 + ks * 8, dQm + ks * ((2 * C::SBO) >> 4), idesc_acc,
+                      (jb > 0 || wh > 0 || ks > 0) ? 1u : 0u);
+            if (wh == 1) {
+              const uint64_t dSm = umma_smem_desc(smem_u32(sDS), 16384, 1024, kSwz128);
+              const uint64_t dKm = umma_smem_desc(smem_u32(sKV + g * 2 * C::TILE_B), C::SBO, C::SBO, C::SWZ);
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks)
+                umma_ss(tbase + C::TM_DQ, dSm + ks * (2048 >> 4), dKm + ks * ((2 * C::SBO) >> 4), idesc_dq,
+                        ks > 0);
+              umma_commit(bar(C::B_QDOEMPTY + s));
+              umma_commit(bar(C::B_DQDONE));
+            }
+            if (t + 1 < T) ok = issue_sdp(tt + 1, (t + 1) % Gc, wh, wh == 0);
+          }
+        }
+        if (ok) {
+          umma_commit(bar(C::B_ACCFULL));
+          umma_commit(bar(C::B_KVFREE));
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ compute warpgroups
+    const int wh = warp >> 2;                 // which 64-query half of the tile
+    const int key = (warp & 3) * 32 + lane;   // key row of the block == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tST = tbase + C::TM_ST + wh * 64 + lane_off;
+    const uint32_t tDP = tbase + C::TM_DP + wh * 64 + lane_off;
+    float* plane = p.planes + (static_cast<long long>(r) * p.BH + bh) * p.L2 * p.L2;
+    bool ok = true;
+    int tt = 0, nb = 0;
+    for (int n = 0; n < ngroups && ok; ++n) {
+      const int i0 = (r + n * p.NP) * G;
+      const int Gc = min(G, p.L1 - i0);
+      for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
+        float acc[64];
+#pragma unroll
+        for (int c = 0; c < 64; ++c) acc[c] = 0.f;
+        const int bs = nb & 1;
+        ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
+        if (!ok) break;
+        const uint8_t* bcol = sBias + bs * C::BIAS_B + (wh * 64) * 256 + key * 2;
+        for (int g = 0; g < Gc; ++g, ++tt) {
+          const int s = tt % C::NQ;
+          const uint8_t* st = sQDO + s * C::STAGE_B;
+          ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
+          if (!ok) break;
+          ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // lse / delta visible
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (wh == 1 && !(jb == 0 && g == 0)) {
+            // dQ of the previous tile of this group is complete: reduce it into the fp32 buffer
+            const int pt = jb * Gc + g - 1;
+            const int pjb = pt / Gc, pg = pt % Gc;
+            float* dst = p.dq32 +
+                         ((static_cast<long long>(bh) * p.L1 + i0 + pg) * p.L2 + pjb * 128 + key) * kD;
+#pragma unroll
+            for (int c = 0; c < kD / 32; ++c) {
+              uint32_t qv[32];
+              tmem_ld32(tbase + C::TM_DQ + c * 32 + lane_off, qv);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                red_add_v4(dst + c * 32 + j * 4, __uint_as_float(qv[4 * j]), __uint_as_float(qv[4 * j + 1]),
+                           __uint_as_float(qv[4 * j + 2]), __uint_as_float(qv[4 * j + 3]));
+            }
+          }
+          if (tt > 0) {  // dS staging buffer free again (the previous dQ MMA has read it)
+            ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
+            if (!ok) break;
+          }
+          const float* lse_s = reinterpret_cast<const float*>(st + 2 * C::TILE_B) + wh * 64;
+          const float* del_s = reinterpret_cast<const float*>(st + 2 * C::TILE_B + 512) + wh * 64;
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t sv[32], dv[32];
+            tmem_ld32(tST + cc * 32, sv);
+            tmem_ld32(tDP + cc * 32, dv);
+            tmem_ld_wait();
+            uint32_t pp[16], dd[16];
+#pragma unroll
+            for (int c2 = 0; c2 < 16; ++c2) {
+              const int q0 = cc * 32 + 2 * c2;
+              const float2 ls = *reinterpret_cast<const float2*>(lse_s + q0);
+              const float2 de = *reinterpret_cast<const float2*>(del_s + q0);
+              const float b0 = ld16_as_float<kBf16>(bcol + q0 * 256);
+              const float b1 = ld16_as_float<kBf16>(bcol + (q0 + 1) * 256);
+              const float x0 = fmaf(__uint_as_float(sv[2 * c2]), p.c1, fmaf(b0, kLog2e, -ls.x));
+              const float x1 = fmaf(__uint_as_float(sv[2 * c2 + 1]), p.c1, fmaf(b1, kLog2e, -ls.y));
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              const float ds0 = p0 * (__uint_as_float(dv[2 * c2]) - de.x);
+              const float ds1 = p1 * (__uint_as_float(dv[2 * c2 + 1]) - de.y);
+              acc[q0] += ds0;
+              acc[q0 + 1] += ds1;
+              pp[c2] = pack2<kBf16>(p0, p1);
+              dd[c2] = pack2<kBf16>(ds0, ds1);
+            }
+            tmem_st16(tST + cc * 16, pp);
+            tmem_st16(tDP + cc * 16, dd);
+            // dS^T row of this key into the M-major staging tile (128-byte swizzle)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 v4 = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
+              *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + (((cc * 4 + j) ^ (key & 7)) << 4)) = v4;
+            }
+          }
+          tmem_st_wait();
+          fence_proxy_async_smem();
+          tc_fence_before_sync();
+          mbar_arrive(bar(C::B_PFULL + wh));
+        }
+        if (!ok) break;
+        // bias stage no longer needed by this warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
+        // dBias: add this CTA's sums over the G rows to its private plane
+        float* dst = plane + (static_cast<long long>(jb) * 128 + wh * 64) * p.L2 + kb * 128 + key;
+        if (n == 0) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) dst[static_cast<long long>(c) * p.L2] = acc[c];
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) red_add(dst + static_cast<long long>(c) * p.L2, acc[c]);
+        }
+      }
+      if (!ok) break;
+      // ---- group epilogue: last dQ tile, then dK / dV of the G rows
+      ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
+      if (!ok) break;
+      tc_fence_after_sync();
+      if (wh == 1) {
+        const int pt = nq * Gc - 1;
+        const int pjb = pt / Gc, pg = pt % Gc;
+        float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + i0 + pg) * p.L2 + pjb * 128 + key) * kD;
+#pragma unroll
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t qv[32];
+          tmem_ld32(tbase + C::TM_DQ + c * 32 + lane_off, qv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            red_add_v4(dst + c * 32 + j * 4, __uint_as_float(qv[4 * j]), __uint_as_float(qv[4 * j + 1]),
+                       __uint_as_float(qv[4 * j + 2]), __uint_as_float(qv[4 * j + 3]));
+        }
+      }
+      {
+        // warpgroup 0 stores dV, warpgroup 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518)
+        const long long* sd = (wh == 0) ? p.sdv : p.sdk;
+        uint16_t* base = reinterpret_cast<uint16_t*>(wh == 0 ? p.dv : p.dk) + b * sd[0] + h * sd[1] +
+                         static_cast<long long>(kb * 128 + key) * sd[3];
+        const float mul = (wh == 0) ? 1.0f : p.scale;
+        for (int g = 0; g < Gc; ++g) {
+          uint16_t* optr = base + static_cast<long long>(i0 + g) * sd[2];
+          const uint32_t ta = tbase + C::TM_ACC + g * 2 * kD + (wh == 0 ? kD : 0) + lane_off;
+#pragma unroll
+          for (int c = 0; c < kD / 32; ++c) {
+            uint32_t av[32];
+            tmem_ld32(ta + c * 32, av);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint4 ov;
+              ov.x = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 0]) * mul, __uint_as_float(av[v4 * 8 + 1]) * mul);
+              ov.y = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 2]) * mul, __uint_as_float(av[v4 * 8 + 3]) * mul);
+              ov.z = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 4]) * mul, __uint_as_float(av[v4 * 8 + 5]) * mul);
+              ov.w = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 6]) * mul, __uint_as_float(av[v4 * 8 + 7]) * mul);
+              *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar(C::B_ACCFREE));
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) __nanosleep(20000);
+  if (warp == 9) tmem_dealloc(tbase, 512);
+}
+
+template <int kD, bool kBf16>
+int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
+  using C = BwdCfg<kD>;
+  static bool attr_set = false;
+  auto kern = fta_bwd_kernel<kD, kBf16>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return -1;
+    attr_set = true;
+  }
+  BwdParams p;
+  p.lse = a.lse;
+  p.delta = a.delta;
+  p.dq32 = a.dq32;
+  p.dk = a.dk;
+  p.dv = a.dv;
+  p.planes = a.planes;
+  p.status = a.status;
+  p.H = a.H;
+  p.L1 = a.L1;
+  p.L2 = a.L2;
+  p.NP = NP;
+  p.BH = a.B * a.H;
+  for (int i = 0; i < 4; ++i) {
+    p.sdk[i] = a.sdk[i];
+    p.sdv[i] = a.sdv[i];
+  }
+  p.c1 = a.sm_scale * kLog2e;
+  p.scale = a.sm_scale;
+  const int grid = a.B * a.H * NP * (a.L2 / 128);
+  kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBias, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace
+
+int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
+
+// Number of private dBias planes == number of row-group residue classes. Chosen so that the
+// grid (B*H * L2/128 * NP CTAs, one per SM at a time) fills whole waves of the device with
+// chains of nearly equal length.
+int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms) {
+  const int G = bwd_rows_per_cta(D);
+  const int ngroups = (L1 + G - 1) / G;
+  const long long base = static_cast<long long>(B) * H * (L2 / 128);
+  int best = 1;
+  double best_eff = -1.0;
+  const int np_max = ngroups < 64 ? ngroups : 64;
+  for (int np = 1; np <= np_max; ++np) {
+    const long long ctas = base * np;
+    const long long waves = (ctas + num_sms - 1) / num_sms;
+    const int chain = (ngroups + np - 1) / np;  // longest chain
+    // time ~ waves * chain ; work ~ base * ngroups / num_sms
+    const double eff = (static_cast<double>(base) * ngroups / num_sms) / (static_cast<double>(waves) * chain);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = np;
+    }
+  }
+  return best;
+}
+
+int launch_bwd(const BwdArgs& a, cudaStream_t stream) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int NP = bwd_num_planes(a.B, a.H, a.L1, a.L2, a.D, sms);
+  if (a.D == 32) return a.bf16 ? launch_bwd_t<32, true>(a, NP, stream) : launch_bwd_t<32, false>(a, NP, stream);
+  return a.bf16 ? launch_bwd_t<64, true>(a, NP, stream) : launch_bwd_t<64, false>(a, NP, stream);
+}
+
+}  // namespace fta

@@ -1,0 +1,54 @@
+// Internal launch interface between the C ABI (api.cu) and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fta {
+
+struct FwdArgs {
+  CUtensorMap tmQ, tmK, tmV, tmBias;
+  void* o;
+  float* lse;
+  int* status;
+  int B, H, L1, L2, D;
+  bool bf16;
+  long long so[4];  // element strides of O over (B, H, L1, L2)
+  float sm_scale;
+};
+int launch_fwd(const FwdArgs& a, cudaStream_t stream);
+int fwd_rows_per_cta(int D);
+
+struct BwdArgs {
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmBias;
+  const float* lse;    // (B,H,L1,L2)
+  const float* delta;  // (B,H,L1,L2)
+  float* dq32;         // (B,H,L1,L2,D) float32, zeroed; receives sum over key blocks of dS K
+  void* dk;
+  void* dv;
+  float* planes;  // (nplanes, B*H, L2, L2) float32 partial dBias
+  int* status;
+  int B, H, L1, L2, D;
+  bool bf16;
+  long long sdk[4], sdv[4];  // element strides of dK, dV over (B, H, L1, L2)
+  float sm_scale;
+};
+int launch_bwd(const BwdArgs& a, cudaStream_t stream);
+int bwd_rows_per_cta(int D);
+int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms);
+
+// delta[row] = sum_d O[row,d] * dO[row,d]
+int launch_preprocess(const void* o, const long long so[4], const void* dout, const long long sdo[4],
+                      float* delta, int B, int H, int L1, int L2, int D, bool bf16,
+                      cudaStream_t stream);
+
+// out_f32[e] = sum_p planes[p][e] (fixed order), optional rounded copy
+int launch_dbias_finalize(const float* planes, int nplanes, long long plane_elems, float* out_f32,
+                          void* out_cast, bool bf16, cudaStream_t stream);
+
+// dq[row, d] = (dtype)(scale * dq32[row, d])
+int launch_dq_finalize(const float* dq32, void* dq, const long long sdq[4], int B, int H, int L1,
+                       int L2, int D, float scale, bool bf16, cudaStream_t stream);
+
+}  // namespace fta

@@ -1,0 +1,372 @@
+// Forward triangle attention for sm_100a: O = softmax(sm_scale * q k^T + bias) v and the
+// base-2 log-sum-exp, the work of the reference's `_attn_fwd` (flash_tt_attn.py:128-264).
+//
+// One CTA owns a 128-query block `jb` of a group of up to G consecutive L1 rows of one
+// (b,h). It walks the key blocks once (outer loop) and, inside, the G rows (inner loop), so
+// that one 128x128 bias tile staged in shared memory serves G score tiles:
+//
+//   warp 8      : TMA producer  (Q tiles once, K/V ring, bias double buffer)
+//   warp 9      : tcgen05 issuer (S = Q K^T into TMEM, O += P V with P read from TMEM)
+//   warps 10-11 : idle (registers are allotted per 4 warps, so they cost nothing)
+//   warps 0-3   : softmax warpgroup 0 -> even rows of the group, S buffer 0
+//   warps 4-7   : softmax warpgroup 1 -> odd rows of the group,  S buffer 1
+//
+// TMEM (512 columns): S buffers 2 x 128 fp32 columns (P overwrites the first 64 columns of
+// its S buffer as packed 16-bit pairs), O accumulators G x D columns.
+// Online softmax state (running max, running sum) lives in registers of the thread that
+// owns the query row; the O accumulator is rescaled lazily (only when the row max grew by
+// more than 2^8), by the same thread, before P is handed to the PV MMA.
+#include "fta_kernels.h"
+#include "tc05.cuh"
+
+namespace fta {
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int kD>
+struct FwdCfg {
+  static constexpr int G = (kD == 32) ? 8 : 4;       // rows per CTA (even)
+  static constexpr int NSTAGE = (kD == 32) ? 4 : 3;  // K/V ring depth
+  static constexpr int TILE_B = 128 * kD * 2;        // one 128 x D tile of 16-bit values
+  static constexpr int BIAS_B = 128 * 128 * 2;       // one 128 x 128 bias tile
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_KV = OFF_Q + G * TILE_B;
+  static constexpr int OFF_BIAS = OFF_KV + NSTAGE * 2 * TILE_B;
+  static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_B;
+  // barrier slots
+  static constexpr int B_QFULL = 0;
+  static constexpr int B_KVFULL = B_QFULL + G;
+  static constexpr int B_KVEMPTY = B_KVFULL + NSTAGE;
+  static constexpr int B_BIASFULL = B_KVEMPTY + NSTAGE;
+  static constexpr int B_BIASEMPTY = B_BIASFULL + 2;
+  static constexpr int B_SFULL = B_BIASEMPTY + 2;
+  static constexpr int B_PFULL = B_SFULL + 2;
+  static constexpr int B_PVDONE = B_PFULL + 2;
+  static constexpr int NBAR = B_PVDONE + 2;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;  // + tmem slot/abort + align slack
+  static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
+  static constexpr uint32_t SBO = 8 * kD * 2;  // bytes between 8-row groups of a tile
+  static constexpr uint32_t TMEM_O = 256;      // first O column
+};
+
+struct FwdParams {
+  void* o;
+  float* lse;
+  int* status;
+  int H, L1, L2;
+  long long so_b, so_h, so_i, so_j;  // element strides of O (D stride is 1)
+  float c1;                          // sm_scale * log2(e)
+};
+
+template <int N>
+__device__ __forceinline__ float sel(const float (&a)[N], int idx) {
+  float r = a[0];
+#pragma unroll
+  for (int i = 1; i < N; ++i) r = (idx == i) ? a[i] : r;
+  return r;
+}
+template <int N>
+__device__ __forceinline__ void put(float (&a)[N], int idx, float v) {
+#pragma unroll
+  for (int i = 0; i < N; ++i) a[i] = (idx == i) ? v : a[i];
+}
+
+template <int kD, bool kBf16>
+__global__ void __launch_bounds__(384, 1)
+fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
+               const FwdParams p) {
+  using C = FwdCfg<kD>;
+  constexpr int G = C::G;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem + C::OFF_Q;
+  uint8_t* sKV = smem + C::OFF_KV;
+  uint8_t* sBias = smem + C::OFF_BIAS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x, ig = blockIdx.y, bh = blockIdx.z;
+  const int b = bh / p.H, h = bh % p.H;
+  const int i0 = ig * G;
+  const int Gc = min(G, p.L1 - i0);
+  const int Gp = (Gc + 1) & ~1;  // rows processed (an odd tail is padded with a zero row)
+  const int nkb = p.L2 / 128;
+  const int T = nkb * Gp;
+  const WaitCtx w{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < G; ++i) mbar_init(bar(C::B_QFULL + i), 1);
+    for (int i = 0; i < C::NSTAGE; ++i) {
+      mbar_init(bar(C::B_KVFULL + i), 1);
+      mbar_init(bar(C::B_KVEMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(C::B_BIASFULL + i), 1);
+      mbar_init(bar(C::B_BIASEMPTY + i), 8);  // one arrive per softmax warp
+      mbar_init(bar(C::B_SFULL + i), 1);
+      mbar_init(bar(C::B_PFULL + i), 128);  // every thread of the warpgroup
+      mbar_init(bar(C::B_PVDONE + i), 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tbase = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmBias);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int bs = kb & 1;
+        ok = mbar_wait(bar(C::B_BIASEMPTY + bs), ((kb >> 1) & 1) ^ 1, w, 1);
+        if (!ok) break;
+        mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
+        tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128,
+                    jb * 128, h, b);
+        tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBias, bar(C::B_BIASFULL + bs),
+                    kb * 128 + 64, jb * 128, h, b);
+        for (int g = 0; g < Gp; ++g) {
+          if (kb == 0) {
+            mbar_expect_tx(bar(C::B_QFULL + g), C::TILE_B);
+            tma_load_5d(smem_u32(sQ + g * C::TILE_B), &tmQ, bar(C::B_QFULL + g), 0, jb * 128,
+                        i0 + g, h, b);
+          }
+          const int t = kb * Gp + g;
+          const int s = t % C::NSTAGE;
+          ok = mbar_wait(bar(C::B_KVEMPTY + s), ((t / C::NSTAGE) & 1) ^ 1, w, 2);
+          if (!ok) break;
+          mbar_expect_tx(bar(C::B_KVFULL + s), 2 * C::TILE_B);
+          tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL + s), 0, kb * 128,
+                      i0 + g, h, b);
+          tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL + s), 0,
+                      kb * 128, i0 + g, h, b);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_f16(kBf16 ? 1 : 0, 128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_f16(kBf16 ? 1 : 0, 128, kD, 0, 1);
+      bool ok = true;
+      auto issue_qk = [&](int t) -> bool {
+        const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE;
+        if (kb == 0 && !mbar_wait(bar(C::B_QFULL + g), 0, w, 3)) return false;
+        if (!mbar_wait(bar(C::B_KVFULL + s), (t / C::NSTAGE) & 1, w, 4)) return false;
+        tc_fence_after_sync();
+        const uint64_t dq = umma_smem_desc(smem_u32(sQ + g * C::TILE_B), 16, C::SBO, C::SWZ);
+        const uint64_t dk = umma_smem_desc(smem_u32(sKV + s * 2 * C::TILE_B), 16, C::SBO, C::SWZ);
+#pragma unroll
+        for (int ks = 0; ks < kD / 16; ++ks)
+          umma_ss(tbase + (g & 1) * 128, dq + ks * 2, dk + ks * 2, idesc_qk, ks > 0);
+        umma_commit(bar(C::B_SFULL + (g & 1)));
+        return true;
+      };
+      ok = issue_qk(0) && issue_qk(1);
+      for (int t = 0; t < T && ok; ++t) {
+        const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE, wb = g & 1;
+        const int n = kb * (Gp >> 1) + (g >> 1);  // tile index within this S buffer
+        ok = mbar_wait(bar(C::B_PFULL + wb), n & 1, w, 5);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint64_t dv =
+            umma_smem_desc(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), C::SBO, C::SBO, C::SWZ);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tbase + C::TMEM_O + g * kD, tbase + wb * 128 + ks * 8,
+                  dv + ks * ((2 * C::SBO) >> 4), idesc_pv, (kb > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(bar(C::B_KVEMPTY + s));
+        umma_commit(bar(C::B_PVDONE + wb));
+        if (t + 2 < T) ok = issue_qk(t + 2);
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int wg = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;  // query row of the tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tbase + wg * 128 + lane_off;
+    float m_used[G / 2], l_run[G / 2];
+#pragma unroll
+    for (int i = 0; i < G / 2; ++i) {
+      m_used[i] = -INFINITY;
+      l_run[i] = 0.f;
+    }
+    const int ngi = Gp >> 1;
+    int n = 0;
+    bool ok = true;
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      const int bs = kb & 1;
+      const uint8_t* brow = sBias + bs * C::BIAS_B + row * 128;
+      for (int gi = 0; gi < ngi; ++gi, ++n) {
+        const int g = 2 * gi + wg;
+        ok = mbar_wait_warp(bar(C::B_SFULL + wg), n & 1, w, 6);
+        if (!ok) break;
+        if (gi == 0) {
+          ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (kb >> 1) & 1, w, 7);
+          if (!ok) break;
+        }
+        tc_fence_after_sync();
+        uint32_t sr[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr + c * 32);
+        tmem_ld_wait();
+        // pass 1: t = s*c1 + bias*log2e, row max
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const uint4 bv = *reinterpret_cast<const uint4*>(brow + (c >> 3) * 16384 +
+                                                            (((c & 7) ^ (row & 7)) << 4));
+          const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float b0, b1;
+            unpack2<kBf16>(bw[e], b0, b1);
+            const float t0 = fmaf(b0, kLog2e, __uint_as_float(sr[c * 8 + 2 * e]) * p.c1);
+            const float t1 = fmaf(b1, kLog2e, __uint_as_float(sr[c * 8 + 2 * e + 1]) * p.c1);
+            sr[c * 8 + 2 * e] = __float_as_uint(t0);
+            sr[c * 8 + 2 * e + 1] = __float_as_uint(t1);
+            mx = fmaxf(mx, fmaxf(t0, t1));
+          }
+        }
+        if (gi == ngi - 1) {  // last use of this bias stage by this warp
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
+        }
+        const float m_old = sel(m_used, gi);
+        const float l_old = sel(l_run, gi);
+        const bool need = mx > m_old + 8.0f;  // lazy rescale threshold: 2^8
+        const float m_new = need ? mx : m_old;
+        const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = need ? fast_exp2(m_old - m_safe) : 1.0f;
+        if (kb > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll
+          for (int c = 0; c < kD / 32; ++c) {
+            uint32_t orr[32];
+            const uint32_t ta = tbase + C::TMEM_O + g * kD + c * 32 + lane_off;
+            tmem_ld32(ta, orr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) orr[j] = __float_as_uint(__uint_as_float(orr[j]) * alpha);
+            tmem_st32(ta, orr);
+          }
+        }
+        // pass 2: p = 2^(t - m), row sum, pack, hand P to the tensor core through TMEM
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = fast_exp2(__uint_as_float(sr[c * 32 + 2 * j]) - m_safe);
+            const float p1 = fast_exp2(__uint_as_float(sr[c * 32 + 2 * j + 1]) - m_safe);
+            sum0 += p0;
+            sum1 += p1;
+            pk[j] = pack2<kBf16>(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        mbar_arrive(bar(C::B_PFULL + wg));
+        const float l_new = l_old * alpha + (sum0 + sum1);
+        put(m_used, gi, m_new);
+        put(l_run, gi, l_new);
+
+        if (kb == nkb - 1) {
+          // epilogue of row g: wait for the last PV, normalise, store O and the log-sum-exp
+          ok = mbar_wait_warp(bar(C::B_PVDONE + wg), n & 1, w, 8);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const int i = i0 + g;
+          const float inv = 1.0f / l_new;
+          const int j = jb * 128 + row;
+          uint16_t* optr = reinterpret_cast<uint16_t*>(p.o) + b * p.so_b + h * p.so_h +
+                           static_cast<long long>(i) * p.so_i + static_cast<long long>(j) * p.so_j;
+#pragma unroll
+          for (int c = 0; c < kD / 32; ++c) {
+            uint32_t orr[32];
+            tmem_ld32(tbase + C::TMEM_O + g * kD + c * 32 + lane_off, orr);
+            tmem_ld_wait();
+            if (i < p.L1) {
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                uint4 ov;
+                ov.x = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 0]) * inv, __uint_as_float(orr[v4 * 8 + 1]) * inv);
+                ov.y = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2]) * inv, __uint_as_float(orr[v4 * 8 + 3]) * inv);
+                ov.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * inv, __uint_as_float(orr[v4 * 8 + 5]) * inv);
+                ov.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * inv, __uint_as_float(orr[v4 * 8 + 7]) * inv);
+                *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
+              }
+            }
+          }
+          if (i < p.L1)
+            p.lse[(static_cast<long long>(bh) * p.L1 + i) * p.L2 + j] = m_safe + log2f(l_new);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) __nanosleep(20000);  // let copies already in flight land before the CTA exits
+  if (warp == 9) tmem_dealloc(tbase, 512);
+}
+
+template <int kD, bool kBf16>
+int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
+  using C = FwdCfg<kD>;
+  static bool attr_set = false;
+  auto kern = fta_fwd_kernel<kD, kBf16>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
+        cudaSuccess)
+      return -1;
+    attr_set = true;
+  }
+  FwdParams p;
+  p.o = a.o;
+  p.lse = a.lse;
+  p.status = a.status;
+  p.H = a.H;
+  p.L1 = a.L1;
+  p.L2 = a.L2;
+  p.so_b = a.so[0];
+  p.so_h = a.so[1];
+  p.so_i = a.so[2];
+  p.so_j = a.so[3];
+  p.c1 = a.sm_scale * kLog2e;
+  dim3 grid(a.L2 / 128, (a.L1 + C::G - 1) / C::G, a.B * a.H);
+  kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmBias, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace
+
+int launch_fwd(const FwdArgs& a, cudaStream_t stream) {
+  if (a.D == 32) return a.bf16 ? launch_fwd_t<32, true>(a, stream) : launch_fwd_t<32, false>(a, stream);
+  return a.bf16 ? launch_fwd_t<64, true>(a, stream) : launch_fwd_t<64, false>(a, stream);
+}
+
+int fwd_rows_per_cta(int D) { return D == 32 ? FwdCfg<32>::G : FwdCfg<64>::G; }
+
+}  // namespace fta

@@ -1,0 +1,164 @@
+"""Drop-in for the reference module ``flash_tt_attn``: ``attention(q, k, v, b_pw, sm_scale)``.
+
+Same entry point, argument meaning and autograd behaviour as the reference's
+``_attention`` / ``attention = _attention.apply`` (flash_tt_attn.py:554-663), with the three
+Triton launches replaced by hand-written sm_100a kernels reached through the C ABI of
+``libfta.so`` (include/fta.h):
+
+  forward   : ``_attn_fwd[grid](...)``              (577-586)  -> ``fta_forward``
+  backward  : ``_attn_bwd_preprocess[pre_grid]``    (636-641)  -> ``fta_bwd_preprocess``
+              ``_attn_bwd[grid]`` + ``zeros_like``  (613, 647-658) -> ``fta_backward``
+
+Differences from the reference, all relaxations:
+  * fp16 and bf16 (the reference is fp16 only, line 99); L1 may differ from L2 (the reference
+    needs a square pair representation, lines 584 and 616); L2 must be a multiple of 128 but
+    need not be a power of two (line 618);
+  * ``dO`` and non-dense inputs are made contiguous instead of asserted on (604-606);
+  * dBias is accumulated in float32 in a fixed order (bit-reproducible) and rounded once,
+    instead of fp16 atomics (425-426);
+  * an optional ``group`` (a ``torch.distributed`` process group): q, k, v hold this rank's
+    shard of the L1 rows, the bias is replicated, and the backward all-reduces the float32
+    dBias over the group before rounding.
+
+There is no fallback: without a CUDA device and a built ``libfta.so`` every call raises.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+import _cabi
+from _cabi import FtaProblem, check, t4, t5
+
+__all__ = ["attention", "reference_tt_attn", "check_device_status", "last_dbias_f32"]
+
+_DEBUG = os.environ.get("FTA_DEBUG", "0") == "1"
+_status_words = {}
+_last = {"dbias_f32": None}
+
+
+def _status(device) -> torch.Tensor:
+    key = (device.type, device.index)
+    st = _status_words.get(key)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = st
+    return st
+
+
+def check_device_status(device=None) -> None:
+    """Raise if a kernel of this module reported a device-side error (a bounded wait that ran
+    out). Synchronises the device's current stream."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _status(device)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise RuntimeError(f"flash_tt_attn: device status 0x{code:x} (a bounded device-side wait ran out)")
+
+
+def last_dbias_f32():
+    """The float32 dBias of the most recent backward call (before rounding to the bias dtype)."""
+    return _last["dbias_f32"]
+
+
+def _dense(t: torch.Tensor) -> torch.Tensor:
+    """Inputs the kernels can address directly: unit stride in D, other strides multiples of 8
+    elements, 16-byte aligned base. Anything else is copied."""
+    ok = t.stride(-1) == 1 and all(s % 8 == 0 and s > 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+    return t if ok else t.contiguous()
+
+
+def _problem(q: torch.Tensor) -> FtaProblem:
+    B, H, L1, L2, D = q.shape
+    return FtaProblem(B, H, L1, L2, D, _cabi.FTA_BF16 if q.dtype == torch.bfloat16 else _cabi.FTA_FP16)
+
+
+class _attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, b_pw, sm_scale, group=None):
+        HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
+        assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
+        assert HEAD_DIM_K in {32, 64}, "head dimension must be 32 or 64"
+        assert q.dtype == k.dtype == v.dtype == b_pw.dtype
+        assert q.dtype in (torch.float16, torch.bfloat16), "fp16 or bf16 only"
+        assert q.is_cuda, "flash_tt_attn.attention needs CUDA tensors (there is no CPU path)"
+        assert q.dim() == 5 and q.shape == k.shape == v.shape
+        B, H, L1, L2, D = q.shape
+        assert b_pw.shape == (B, H, L2, L2), "bias must be (B, H, L2, L2)"
+        assert L2 % 128 == 0, "L2 must be a multiple of 128"
+
+        q, k, v, b_pw = _dense(q), _dense(k), _dense(v), _dense(b_pw)
+        o = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((B, H, L1, L2), dtype=torch.float32, device=q.device)
+        status = _status(q.device)
+        prob = _problem(q)
+        with torch.cuda.device(q.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            check(_cabi.lib().fta_forward(prob, t5(q), t5(k), t5(v), t4(b_pw), float(sm_scale), t5(o),
+                                          lse.data_ptr(), status.data_ptr(), stream), "fta_forward")
+        if _DEBUG:
+            check_device_status(q.device)
+        ctx.save_for_backward(q, k, v, o, b_pw, lse)
+        ctx.sm_scale = float(sm_scale)
+        ctx.group = group
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, b_pw, lse = ctx.saved_tensors
+        assert do.dtype == q.dtype
+        do = _dense(do)
+        B, H, L1, L2, D = q.shape
+        dev = q.device
+        dq = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=dev)
+        dk = torch.empty_like(dq)
+        dv = torch.empty_like(dq)
+        db = torch.empty((B, H, L2, L2), dtype=b_pw.dtype, device=dev)
+        db32 = torch.empty((B, H, L2, L2), dtype=torch.float32, device=dev)
+        delta = torch.empty_like(lse)
+        prob = _problem(q)
+        L = _cabi.lib()
+        ws_bytes = int(L.fta_bwd_workspace_bytes(prob))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        status = _status(dev)
+        sharded = ctx.group is not None
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream().cuda_stream
+            check(L.fta_bwd_preprocess(prob, t5(o), t5(do), delta.data_ptr(), stream), "fta_bwd_preprocess")
+            check(L.fta_backward(prob, t5(q), t5(k), t5(v), t4(b_pw), t5(do), lse.data_ptr(), delta.data_ptr(),
+                                 ctx.sm_scale, t5(dq), t5(dk), t5(dv), db32.data_ptr(),
+                                 None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
+                                 status.data_ptr(), stream), "fta_backward")
+            if sharded:
+                # the only collective of the path: sum the per-rank partial dBias over NVLink
+                torch.distributed.all_reduce(db32, op=torch.distributed.ReduceOp.SUM, group=ctx.group)
+                check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
+                      "fta_dbias_cast")
+        if _DEBUG:
+            check_device_status(dev)
+        _last["dbias_f32"] = db32
+        return dq, dk, dv, db, None, None
+
+
+def attention(q, k, v, b_pw, sm_scale, group=None):
+    """Fused triangle attention: ``softmax(q k^T * sm_scale + b_pw) v`` for q, k, v of shape
+    (B, H, L1, L2, D) and a pair bias (B, H, L2, L2) shared by the L1 rows; differentiable in
+    q, k, v and b_pw (dBias is summed over L1). See the module docstring."""
+    return _attention.apply(q, k, v, b_pw, sm_scale, group)
+
+
+def reference_tt_attn(q, k, v, b, sm_scale):
+    """Naive PyTorch statement of the op (what the reference's function of the same name
+    computes, flash_tt_attn.py:845-864): logits in the input dtype, softmax in float32, the
+    probabilities cast back to ``v.dtype``. Materialises (B,H,L1,L2,L2); for checks only."""
+    logits = torch.einsum("bhijd,bhikd->bhijk", q, k) * sm_scale + b.unsqueeze(2)
+    p = torch.softmax(logits.float(), dim=-1).to(v.dtype)
+    return torch.einsum("bhijk,bhikd->bhijd", p, v)
+
+
+def shard_rows(L1: int, rank: int, world: int) -> slice:
+    """Contiguous block of L1 rows owned by ``rank`` (rows are independent problems)."""
+    per = (L1 + world - 1) // world
+    return slice(min(L1, rank * per), min(L1, (rank + 1) * per))

@@ -1,0 +1,134 @@
+/* libfta: B200 (sm_100a) triangle attention, C ABI.
+ *
+ * Drop-in kernels for the hot path of BryanZWu/flash-triangle-attention: the three Triton
+ * launches behind `flash_tt_attn.attention` (forward; backward preprocess + backward).
+ * For q, k, v of shape (B,H,L1,L2,D) and a pair bias of shape (B,H,L2,L2) shared by the L1
+ * rows:
+ *     S = sm_scale * q k^T + bias ;  P = softmax_k(S) ;  O = P v
+ *     dV = P^T dO ; dP = dO v^T ; dS = P (dP - rowsum(dO O))
+ *     dQ = sm_scale dS k ; dK = sm_scale dS^T q ; dBias = sum over L1 of dS
+ *
+ * Conventions
+ *  - plain pointers, sizes and element strides; no framework types;
+ *  - every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise;
+ *  - the library never allocates or frees device memory: outputs, the log-sum-exp, the
+ *    workspace and the status word belong to the caller;
+ *  - all work is enqueued on `stream` (a cudaStream_t passed as void*); calls return
+ *    without synchronising;
+ *  - return value 0 on success, a negative FTA_ERR_* otherwise; bad arguments are rejected
+ *    on the host before anything is launched; nothing traps or asserts on the device;
+ *  - device-side waits are bounded; a wait that runs out writes a non-zero code to the
+ *    caller's status word (see fta_read_status) and the kernel returns;
+ *  - supported: dtype fp16 / bf16 (q, k, v, bias, o, dO and the gradients share it),
+ *    D in {32, 64}, L2 a multiple of 128, any L1 >= 1 (L1 != L2 is fine: a shard of rows),
+ *    innermost (D) stride 1 and 16-byte aligned rows.
+ */
+#ifndef FTA_H_
+#define FTA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define FTA_API __attribute__((visibility("default")))
+#else
+#define FTA_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { FTA_FP16 = 0, FTA_BF16 = 1 };
+
+enum {
+  FTA_OK = 0,
+  FTA_ERR_NULL = -1,       /* a required pointer is NULL */
+  FTA_ERR_SHAPE = -2,      /* non-positive size, or L2 not a multiple of 128 */
+  FTA_ERR_HEAD_DIM = -3,   /* D not in {32, 64} */
+  FTA_ERR_DTYPE = -4,      /* dtype not FTA_FP16 / FTA_BF16 */
+  FTA_ERR_STRIDE = -5,     /* D stride != 1, or a stride that is not a multiple of 8 elements */
+  FTA_ERR_ALIGN = -6,      /* base pointer not 16-byte aligned */
+  FTA_ERR_WORKSPACE = -7,  /* workspace too small */
+  FTA_ERR_TENSOR_MAP = -8, /* the driver refused a TMA tensor map */
+  FTA_ERR_CUDA = -9,       /* a CUDA runtime call failed (see fta_last_cuda_error) */
+  FTA_ERR_DEVICE = -10,    /* status word non-zero: a bounded device wait ran out */
+  FTA_ERR_TOO_LARGE = -11  /* size beyond a documented maximum */
+};
+
+typedef struct FtaProblem {
+  int32_t B, H, L1, L2, D;
+  int32_t dtype; /* FTA_FP16 or FTA_BF16 */
+} FtaProblem;
+
+/* (B,H,L1,L2,D) tensor: base pointer + element strides of the five dimensions. */
+typedef struct FtaTensor5 {
+  void* ptr;
+  int64_t stride[5];
+} FtaTensor5;
+
+/* (B,H,L2,L2) pair bias: base pointer + element strides (query index, then key index). */
+typedef struct FtaTensor4 {
+  void* ptr;
+  int64_t stride[4];
+} FtaTensor4;
+
+/* Library version (major*10000 + minor*100 + patch). */
+FTA_API int fta_version(void);
+
+/* Text for an FTA_ERR_* code. Never NULL. */
+FTA_API const char* fta_strerror(int code);
+
+/* cudaError_t of the last failing CUDA call made by this library on this thread. */
+FTA_API int fta_last_cuda_error(void);
+
+/* Forward pass. Replaces the `_attn_fwd` launch of `_attention.forward`
+ * (flash_tt_attn.py:556-593, kernel 128-264): writes O (same dtype as q) and the base-2
+ * log-sum-exp of the scaled, biased logits, `lse` (B,H,L1,L2) float32 contiguous, which is
+ * what the reference saves for its backward (flash_tt_attn.py:258-263).
+ * `status` points to one int32 the caller zeroed. */
+FTA_API int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
+                const FtaTensor5* v, const FtaTensor4* bias, float sm_scale,
+                const FtaTensor5* o, float* lse, int32_t* status, void* stream);
+
+/* Backward preprocess. Replaces `_attn_bwd_preprocess` (flash_tt_attn.py:266-288, launched
+ * at 636-641): delta[b,h,i,j] = sum_d O[b,h,i,j,d] * dO[b,h,i,j,d], float32 contiguous. */
+FTA_API int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const FtaTensor5* dout,
+                       float* delta, void* stream);
+
+/* Bytes of workspace fta_backward needs for `prob` (a float32 dQ accumulator and the
+ * partial dBias planes). 256-byte aligned workspace required. */
+FTA_API size_t fta_bwd_workspace_bytes(const FtaProblem* prob);
+
+/* Number of partial dBias planes the backward kernel produces for `prob` (each plane is
+ * the sum of dS over a fixed group of consecutive L1 rows; they are summed in plane order). */
+FTA_API int fta_bwd_num_planes(const FtaProblem* prob);
+
+/* Backward pass. Replaces the `_attn_bwd` launch and the `zeros_like` dBias buffer of
+ * `_attention.backward` (flash_tt_attn.py:596-660, kernel 442-550). Needs `lse` from
+ * fta_forward and `delta` from fta_bwd_preprocess. Writes dq, dk, dv (dtype of q), the
+ * float32 dBias `dbias_f32` (B,H,L2,L2 contiguous; the sum over this call's L1 rows, in a
+ * fixed order, so bit-reproducible) and, when `dbias_cast` is not NULL, the same rounded to
+ * the bias dtype (what the reference returns, flash_tt_attn.py:613). A caller that shards L1
+ * over several GPUs passes dbias_cast = NULL, sums dbias_f32 over ranks and then calls
+ * fta_dbias_cast. */
+FTA_API int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
+                 const FtaTensor5* v, const FtaTensor4* bias, const FtaTensor5* dout,
+                 const float* lse, const float* delta, float sm_scale, const FtaTensor5* dq,
+                 const FtaTensor5* dk, const FtaTensor5* dv, float* dbias_f32, void* dbias_cast,
+                 void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* dst[i] = (dtype) src[i] for n elements (n a multiple of 4): the final rounding of dBias to
+ * the bias dtype after a cross-GPU sum (the reference accumulates directly in that dtype,
+ * flash_tt_attn.py:425-426, 613). */
+FTA_API int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* stream);
+
+/* Copies the status word to the host and synchronises `stream`. Returns FTA_OK when it is
+ * zero, FTA_ERR_DEVICE otherwise; `*code_out` (host pointer, may be NULL) receives the raw
+ * word: 0x1000 | site for a wait that ran out. */
+FTA_API int fta_read_status(const int32_t* status, int32_t* code_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FTA_H_ */
