@@ -234,4 +234,9 @@ int fta_read_status(const int32_t* status, int32_t* code_out, void* stream) {
   return host == 0 ? FTA_OK : FTA_ERR_DEVICE;
 }
 
+#ifdef FTA_TRACE
+FTA_API int fta_trace_read_fwd(unsigned long long* host, int n) { return fta::trace_read_fwd(host, n); }
+FTA_API int fta_trace_read_bwd(unsigned long long* host, int n) { return fta::trace_read_bwd(host, n); }
+#endif
+
 }  // extern "C"

@@ -34,10 +34,22 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+#ifdef FTA_TRACE
+// Debug build only: clock64() stamps of CTA 0, read back with fta_trace_read_bwd().
+__device__ unsigned long long g_trace_bwd[8192];
+#define FTA_STAMP(role, ev, tile)                                                  \
+  do {                                                                             \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile) < 64)                 \
+      g_trace_bwd[((role) * 64 + (tile)) * 8 + (ev)] = clock64();                  \
+  } while (0)
+#else
+#define FTA_STAMP(role, ev, tile) do { } while (0)
+#endif
+
 template <int kD>
 struct BwdCfg {
   static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + D + 2*D*G <= 512)
-  static constexpr int NQ = 2;                  // Q/dO ring depth
+  static constexpr int NQ = (kD == 32) ? 4 : 2;  // Q/dO ring depth
   static constexpr int TILE_B = 128 * kD * 2;
   static constexpr int STAGE_B = 2 * TILE_B + 1024;  // Q, dO, lse[128], delta[128]
   static constexpr int BIAS_B = 128 * 128 * 2;
@@ -164,9 +176,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tbase = *tmem_slot;
 
-  if (warp >= 8) reg_dec<88>();
-  else reg_inc<208>();
-
+  if (warp >= 8) {
+    reg_dec<88>();
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -249,8 +260,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int jb = t / Gc, g = t % Gc, s = tt % C::NQ;
           const uint8_t* st = sQDO + s * C::STAGE_B;
           for (int wh = 0; wh < 2 && ok; ++wh) {
+            FTA_STAMP(2, wh * 3 + 0, tt);
             ok = mbar_wait(bar(C::B_PFULL + wh), tt & 1, w, 0x33);
             if (!ok) break;
+            FTA_STAMP(2, wh * 3 + 1, tt);
             if (t == 0 && wh == 0 && n > 0) {
               ok = mbar_wait(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
               if (!ok) break;
@@ -279,6 +292,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               umma_commit(bar(C::B_DQDONE));
             }
             if (t + 1 < T) ok = issue_sdp(tt + 1, (t + 1) % Gc, wh, wh == 0);
+            FTA_STAMP(2, wh * 3 + 2, tt);
           }
         }
         if (ok) {
@@ -287,8 +301,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
     }
-  } else if (warp < 8) {
+  }
+  } else {
     // ------------------------------------------------------------------ compute warpgroups
+    reg_inc<208>();
     const int wh = warp >> 2;                 // which 64-query half of the tile
     const int key = (warp & 3) * 32 + lane;   // key row of the block == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -311,8 +327,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int g = 0; g < Gc; ++g, ++tt) {
           const int s = tt % C::NQ;
           const uint8_t* st = sQDO + s * C::STAGE_B;
+          if ((warp & 3) == 0) FTA_STAMP(wh, 0, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
+          if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // lse / delta visible
           if (!ok) break;
           tc_fence_after_sync();
@@ -337,6 +355,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
             if (!ok) break;
           }
+          if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
           const float* lse_s = reinterpret_cast<const float*>(st + 2 * C::TILE_B) + wh * 64;
           const float* del_s = reinterpret_cast<const float*>(st + 2 * C::TILE_B + 512) + wh * 64;
 #pragma unroll
@@ -372,10 +391,12 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + (((cc * 4 + j) ^ (key & 7)) << 4)) = v4;
             }
           }
+          if ((warp & 3) == 0) FTA_STAMP(wh, 3, tt);
           tmem_st_wait();
           fence_proxy_async_smem();
           tc_fence_before_sync();
           mbar_arrive(bar(C::B_PFULL + wh));
+          if ((warp & 3) == 0) FTA_STAMP(wh, 4, tt);
         }
         if (!ok) break;
         // bias stage no longer needed by this warp
@@ -484,6 +505,12 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef FTA_TRACE
+int trace_read_bwd(unsigned long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
 

@@ -51,4 +51,10 @@ int launch_dbias_finalize(const float* planes, int nplanes, long long plane_elem
 int launch_dq_finalize(const float* dq32, void* dq, const long long sdq[4], int B, int H, int L1,
                        int L2, int D, float scale, bool bf16, cudaStream_t stream);
 
+#ifdef FTA_TRACE
+// debug builds only: clock stamps of CTA 0 of the last launch
+int trace_read_fwd(unsigned long long* host, int n);
+int trace_read_bwd(unsigned long long* host, int n);
+#endif
+
 }  // namespace fta

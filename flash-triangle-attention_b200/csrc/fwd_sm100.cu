@@ -7,12 +7,19 @@
 //
 //   warp 8      : TMA producer  (Q tiles once, K/V ring, bias double buffer)
 //   warp 9      : tcgen05 issuer (S = Q K^T into TMEM, O += P V with P read from TMEM)
-//   warps 10-11 : idle (registers are allotted per 4 warps, so they cost nothing)
-//   warps 0-3   : softmax warpgroup 0 -> even rows of the group, S buffer 0
-//   warps 4-7   : softmax warpgroup 1 -> odd rows of the group,  S buffer 1
+//   warps 0-3   : softmax warpgroup 0 -> even rows of the group, S/P buffer 0
+//   warps 4-7   : softmax warpgroup 1 -> odd rows of the group,  S/P buffer 1
+//   warps 10-11 : idle; warps 8-11 form a warpgroup that hands most of its registers to the
+//                 softmax warpgroups (setmaxnreg)
 //
-// TMEM (512 columns): S buffers 2 x 128 fp32 columns (P overwrites the first 64 columns of
-// its S buffer as packed 16-bit pairs), O accumulators G x D columns.
+// The producer and issuer loops run warp-uniformly (all 32 lanes) and only the TMA / MMA
+// instruction itself is issued by one elected lane, so that descriptors and addresses stay
+// in uniform registers.
+//
+// TMEM (512 columns): S buffers 2 x 128 fp32 columns, P buffers 2 x 64 columns (packed
+// 16-bit pairs), O accumulators G x D columns. S and P are separate so that the next
+// S = Q K^T of a warpgroup is issued as soon as the warpgroup has copied its S tile to
+// registers, and is ready when the warpgroup comes back for it.
 // Online softmax state (running max, running sum) lives in registers of the thread that
 // owns the query row; the O accumulator is rescaled lazily (only when the row max grew by
 // more than 2^8), by the same thread, before P is handed to the PV MMA.
@@ -24,11 +31,24 @@ namespace fta {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLazyThreshold = 5.545177444f;  // 8 / log2(e): rescale when the max grew by > 2^8
+
+#ifdef FTA_TRACE
+// Debug build only: clock64() stamps of CTA (0,0,0), read back with fta_trace_read_fwd().
+__device__ unsigned long long g_trace[8192];
+#define FTA_STAMP(role, ev, tile)                                                          \
+  do {                                                                                     \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (tile) < 64) \
+      g_trace[((role) * 64 + (tile)) * 8 + (ev)] = clock64();                              \
+  } while (0)
+#else
+#define FTA_STAMP(role, ev, tile) do { } while (0)
+#endif
 
 template <int kD>
 struct FwdCfg {
-  static constexpr int G = (kD == 32) ? 8 : 4;       // rows per CTA (even)
-  static constexpr int NSTAGE = (kD == 32) ? 4 : 3;  // K/V ring depth
+  static constexpr int G = (kD == 32) ? 4 : 2;       // rows per CTA (even)
+  static constexpr int NSTAGE = (kD == 32) ? 6 : 4;  // K/V ring depth
   static constexpr int TILE_B = 128 * kD * 2;        // one 128 x D tile of 16-bit values
   static constexpr int BIAS_B = 128 * 128 * 2;       // one 128 x 128 bias tile
   static constexpr int OFF_Q = 0;
@@ -42,13 +62,16 @@ struct FwdCfg {
   static constexpr int B_BIASFULL = B_KVEMPTY + NSTAGE;
   static constexpr int B_BIASEMPTY = B_BIASFULL + 2;
   static constexpr int B_SFULL = B_BIASEMPTY + 2;
-  static constexpr int B_PFULL = B_SFULL + 2;
+  static constexpr int B_SFREE = B_SFULL + 2;
+  static constexpr int B_PFULL = B_SFREE + 2;
   static constexpr int B_PVDONE = B_PFULL + 2;
   static constexpr int NBAR = B_PVDONE + 2;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;  // + tmem slot/abort + align slack
   static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
   static constexpr uint32_t SBO = 8 * kD * 2;  // bytes between 8-row groups of a tile
-  static constexpr uint32_t TMEM_O = 256;      // first O column
+  static constexpr uint32_t TMEM_P = 256;      // first P column
+  static constexpr uint32_t TMEM_O = 384;      // first O column
+  static_assert(TMEM_O + G * kD <= 512, "TMEM budget");
 };
 
 struct FwdParams {
@@ -57,7 +80,7 @@ struct FwdParams {
   int* status;
   int H, L1, L2;
   long long so_b, so_h, so_i, so_j;  // element strides of O (D stride is 1)
-  float c1;                          // sm_scale * log2(e)
+  float scale;                       // sm_scale
 };
 
 template <int N>
@@ -89,7 +112,8 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x, ig = blockIdx.y, bh = blockIdx.z;
@@ -112,7 +136,8 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(bar(C::B_BIASFULL + i), 1);
       mbar_init(bar(C::B_BIASEMPTY + i), 8);  // one arrive per softmax warp
       mbar_init(bar(C::B_SFULL + i), 1);
-      mbar_init(bar(C::B_PFULL + i), 128);  // every thread of the warpgroup
+      mbar_init(bar(C::B_SFREE + i), 4);  // one arrive per warp of the warpgroup
+      mbar_init(bar(C::B_PFULL + i), 4);
       mbar_init(bar(C::B_PVDONE + i), 1);
     }
     mbar_fence_init();
@@ -126,85 +151,110 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tbase = *tmem_slot;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmBias);
+  if (warp >= 8) {
+    reg_dec<88>();
+    if (warp == 8) {
+      // ---------------------------------------------------------------- TMA producer
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmBias);
+      }
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int bs = kb & 1;
-        ok = mbar_wait(bar(C::B_BIASEMPTY + bs), ((kb >> 1) & 1) ^ 1, w, 1);
+        ok = mbar_wait_warp(bar(C::B_BIASEMPTY + bs), ((kb >> 1) & 1) ^ 1, w, 1);
         if (!ok) break;
-        mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
-        tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128,
-                    jb * 128, h, b);
-        tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBias, bar(C::B_BIASFULL + bs),
-                    kb * 128 + 64, jb * 128, h, b);
+        if (elect_one()) {
+          mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
+          tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128,
+                      jb * 128, h, b);
+          tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBias, bar(C::B_BIASFULL + bs),
+                      kb * 128 + 64, jb * 128, h, b);
+        }
         for (int g = 0; g < Gp; ++g) {
-          if (kb == 0) {
+          if (kb == 0 && elect_one()) {
             mbar_expect_tx(bar(C::B_QFULL + g), C::TILE_B);
-            tma_load_5d(smem_u32(sQ + g * C::TILE_B), &tmQ, bar(C::B_QFULL + g), 0, jb * 128,
-                        i0 + g, h, b);
+            tma_load_5d(smem_u32(sQ + g * C::TILE_B), &tmQ, bar(C::B_QFULL + g), 0, jb * 128, i0 + g,
+                        h, b);
           }
           const int t = kb * Gp + g;
           const int s = t % C::NSTAGE;
-          ok = mbar_wait(bar(C::B_KVEMPTY + s), ((t / C::NSTAGE) & 1) ^ 1, w, 2);
+          ok = mbar_wait_warp(bar(C::B_KVEMPTY + s), ((t / C::NSTAGE) & 1) ^ 1, w, 2);
           if (!ok) break;
-          mbar_expect_tx(bar(C::B_KVFULL + s), 2 * C::TILE_B);
-          tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL + s), 0, kb * 128,
-                      i0 + g, h, b);
-          tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL + s), 0,
-                      kb * 128, i0 + g, h, b);
+          if (elect_one()) {
+            mbar_expect_tx(bar(C::B_KVFULL + s), 2 * C::TILE_B);
+            tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL + s), 0, kb * 128,
+                        i0 + g, h, b);
+            tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL + s), 0,
+                        kb * 128, i0 + g, h, b);
+          }
         }
       }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 9) {
+      // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = umma_idesc_f16(kBf16 ? 1 : 0, 128, 128, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kBf16 ? 1 : 0, 128, kD, 0, 1);
+      const uint32_t sQ_a = smem_u32(sQ), sKV_a = smem_u32(sKV);
       bool ok = true;
+      // S(t) = Q_g K^T into S buffer g&1, once the buffer's previous tile has been copied
+      // out by its warpgroup.
       auto issue_qk = [&](int t) -> bool {
-        const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE;
-        if (kb == 0 && !mbar_wait(bar(C::B_QFULL + g), 0, w, 3)) return false;
-        if (!mbar_wait(bar(C::B_KVFULL + s), (t / C::NSTAGE) & 1, w, 4)) return false;
+        const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE, wb = g & 1;
+        const int n = kb * (Gp >> 1) + (g >> 1);  // tile index within this S buffer
+        if (kb == 0 && !mbar_wait_warp(bar(C::B_QFULL + g), 0, w, 3)) return false;
+        if (!mbar_wait_warp(bar(C::B_KVFULL + s), (t / C::NSTAGE) & 1, w, 4)) return false;
+        if (n > 0 && !mbar_wait_warp(bar(C::B_SFREE + wb), (n - 1) & 1, w, 9)) return false;
         tc_fence_after_sync();
-        const uint64_t dq = umma_smem_desc(smem_u32(sQ + g * C::TILE_B), 16, C::SBO, C::SWZ);
-        const uint64_t dk = umma_smem_desc(smem_u32(sKV + s * 2 * C::TILE_B), 16, C::SBO, C::SWZ);
+        const uint64_t dq = umma_smem_desc(sQ_a + g * C::TILE_B, 16, C::SBO, C::SWZ);
+        const uint64_t dk = umma_smem_desc(sKV_a + s * 2 * C::TILE_B, 16, C::SBO, C::SWZ);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks)
-          umma_ss(tbase + (g & 1) * 128, dq + ks * 2, dk + ks * 2, idesc_qk, ks > 0);
-        umma_commit(bar(C::B_SFULL + (g & 1)));
+          for (int ks = 0; ks < kD / 16; ++ks)
+            umma_ss(tbase + wb * 128, dq + ks * 2, dk + ks * 2, idesc_qk, ks > 0);
+          umma_commit(bar(C::B_SFULL + wb));
+        }
+        __syncwarp();
         return true;
       };
       ok = issue_qk(0) && issue_qk(1);
       for (int t = 0; t < T && ok; ++t) {
         const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE, wb = g & 1;
-        const int n = kb * (Gp >> 1) + (g >> 1);  // tile index within this S buffer
-        ok = mbar_wait(bar(C::B_PFULL + wb), n & 1, w, 5);
+        const int n = kb * (Gp >> 1) + (g >> 1);
+        if (t + 2 < T) {
+          ok = issue_qk(t + 2);  // waits until S(t) has been copied out
+          if (!ok) break;
+        }
+        FTA_STAMP(2, 0, t);
+        ok = mbar_wait_warp(bar(C::B_PFULL + wb), n & 1, w, 5);
         if (!ok) break;
+        FTA_STAMP(2, 1, t);
         tc_fence_after_sync();
-        const uint64_t dv =
-            umma_smem_desc(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), C::SBO, C::SBO, C::SWZ);
+        const uint64_t dv = umma_smem_desc(sKV_a + s * 2 * C::TILE_B + C::TILE_B, C::SBO, C::SBO, C::SWZ);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_ts(tbase + C::TMEM_O + g * kD, tbase + wb * 128 + ks * 8,
-                  dv + ks * ((2 * C::SBO) >> 4), idesc_pv, (kb > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(bar(C::B_KVEMPTY + s));
-        umma_commit(bar(C::B_PVDONE + wb));
-        if (t + 2 < T) ok = issue_qk(t + 2);
+          for (int ks = 0; ks < 8; ++ks)
+            umma_ts(tbase + C::TMEM_O + g * kD, tbase + C::TMEM_P + wb * 64 + ks * 8,
+                    dv + ks * ((2 * C::SBO) >> 4), idesc_pv, (kb > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(bar(C::B_KVEMPTY + s));
+          umma_commit(bar(C::B_PVDONE + wb));
+        }
+        __syncwarp();
+        FTA_STAMP(2, 2, t);
       }
     }
-  } else if (warp < 8) {
+  } else {
     // ------------------------------------------------------------------ softmax warpgroups
+    reg_inc<208>();
     const int wg = warp >> 2;
     const int row = (warp & 3) * 32 + lane;  // query row of the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + wg * 128 + lane_off;
-    float m_used[G / 2], l_run[G / 2];
+    const uint32_t tP = tbase + C::TMEM_P + wg * 64 + lane_off;
+    const f32x2 scale2 = mk2(p.scale, p.scale);
+    const f32x2 log2e2 = mk2(kLog2e, kLog2e);
+    float m_used[G / 2], l_run[G / 2];  // running max (natural-log units) and running sum
 #pragma unroll
     for (int i = 0; i < G / 2; ++i) {
       m_used[i] = -INFINITY;
@@ -218,19 +268,26 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const uint8_t* brow = sBias + bs * C::BIAS_B + row * 128;
       for (int gi = 0; gi < ngi; ++gi, ++n) {
         const int g = 2 * gi + wg;
+        if ((warp & 3) == 0) FTA_STAMP(wg, 0, n);
         ok = mbar_wait_warp(bar(C::B_SFULL + wg), n & 1, w, 6);
         if (!ok) break;
         if (gi == 0) {
           ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (kb >> 1) & 1, w, 7);
           if (!ok) break;
         }
+        if ((warp & 3) == 0) FTA_STAMP(wg, 1, n);
         tc_fence_after_sync();
         uint32_t sr[128];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sr + c * 32);
         tmem_ld_wait();
-        // pass 1: t = s*c1 + bias*log2e, row max
-        float mx = -INFINITY;
+        // the S buffer may now be overwritten by the next Q K^T of this warpgroup
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_SFREE + wg));
+        if ((warp & 3) == 0) FTA_STAMP(wg, 2, n);
+        // pass 1: x = s*scale + bias (natural-log units), row max
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
           const uint4 bv = *reinterpret_cast<const uint4*>(brow + (c >> 3) * 16384 +
@@ -238,25 +295,31 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float b0, b1;
+            float b0, b1, x0, x1;
             unpack2<kBf16>(bw[e], b0, b1);
-            const float t0 = fmaf(b0, kLog2e, __uint_as_float(sr[c * 8 + 2 * e]) * p.c1);
-            const float t1 = fmaf(b1, kLog2e, __uint_as_float(sr[c * 8 + 2 * e + 1]) * p.c1);
-            sr[c * 8 + 2 * e] = __float_as_uint(t0);
-            sr[c * 8 + 2 * e + 1] = __float_as_uint(t1);
-            mx = fmaxf(mx, fmaxf(t0, t1));
+            const f32x2 x = fma2(mk2(__uint_as_float(sr[c * 8 + 2 * e]), __uint_as_float(sr[c * 8 + 2 * e + 1])),
+                                 scale2, mk2(b0, b1));
+            un2(x, x0, x1);
+            sr[c * 8 + 2 * e] = __float_as_uint(x0);
+            sr[c * 8 + 2 * e + 1] = __float_as_uint(x1);
+            if (e == 0) mx0 = max3(mx0, x0, x1);
+            else if (e == 1) mx1 = max3(mx1, x0, x1);
+            else if (e == 2) mx2 = max3(mx2, x0, x1);
+            else mx3 = max3(mx3, x0, x1);
           }
         }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         if (gi == ngi - 1) {  // last use of this bias stage by this warp
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
         }
+        if ((warp & 3) == 0) FTA_STAMP(wg, 3, n);
         const float m_old = sel(m_used, gi);
         const float l_old = sel(l_run, gi);
-        const bool need = mx > m_old + 8.0f;  // lazy rescale threshold: 2^8
+        const bool need = mx > m_old + kLazyThreshold;
         const float m_new = need ? mx : m_old;
         const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = need ? fast_exp2(m_old - m_safe) : 1.0f;
+        const float alpha = need ? fast_exp2((m_old - m_safe) * kLog2e) : 1.0f;
         if (kb > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll
           for (int c = 0; c < kD / 32; ++c) {
@@ -269,30 +332,46 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tmem_st32(ta, orr);
           }
         }
-        // pass 2: p = 2^(t - m), row sum, pack, hand P to the tensor core through TMEM
-        float sum0 = 0.f, sum1 = 0.f;
+        // the P buffer is free once the PV MMA of this warpgroup's previous tile is done
+        if (n > 0) {
+          ok = mbar_wait_warp(bar(C::B_PVDONE + wg), (n - 1) & 1, w, 10);
+          if (!ok) break;
+        }
+        if ((warp & 3) == 0) FTA_STAMP(wg, 4, n);
+        // pass 2: p = 2^((x - m) * log2e), row sum, pack, hand P to the tensor core through TMEM
+        const float nm = -m_safe * kLog2e;
+        const f32x2 nm2 = mk2(nm, nm);
+        f32x2 sum2a = mk2(0.f, 0.f), sum2b = mk2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float p0 = fast_exp2(__uint_as_float(sr[c * 32 + 2 * j]) - m_safe);
-            const float p1 = fast_exp2(__uint_as_float(sr[c * 32 + 2 * j + 1]) - m_safe);
-            sum0 += p0;
-            sum1 += p1;
+            float y0, y1;
+            un2(fma2(mk2(__uint_as_float(sr[c * 32 + 2 * j]), __uint_as_float(sr[c * 32 + 2 * j + 1])), log2e2, nm2),
+                y0, y1);
+            const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+            if (j & 1) sum2b = add2(sum2b, mk2(p0, p1));
+            else sum2a = add2(sum2a, mk2(p0, p1));
             pk[j] = pack2<kBf16>(p0, p1);
           }
-          tmem_st16(tS + c * 16, pk);
+          tmem_st16(tP + c * 16, pk);
         }
+        float s0, s1;
+        un2(add2(sum2a, sum2b), s0, s1);
+        if ((warp & 3) == 0) FTA_STAMP(wg, 5, n);
         tmem_st_wait();
         tc_fence_before_sync();
-        mbar_arrive(bar(C::B_PFULL + wg));
-        const float l_new = l_old * alpha + (sum0 + sum1);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_PFULL + wg));
+        if ((warp & 3) == 0) FTA_STAMP(wg, 6, n);
+        const float l_new = l_old * alpha + (s0 + s1);
         put(m_used, gi, m_new);
         put(l_run, gi, l_new);
 
         if (kb == nkb - 1) {
-          // epilogue of row g: wait for the last PV, normalise, store O and the log-sum-exp
+          // epilogue of row g: wait for the last PV, normalise, store O and the log-sum-exp.
+          // (Consumes PVDONE phase n; no later tile of this warpgroup waits for it again.)
           ok = mbar_wait_warp(bar(C::B_PVDONE + wg), n & 1, w, 8);
           if (!ok) break;
           tc_fence_after_sync();
@@ -319,7 +398,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
           }
           if (i < p.L1)
-            p.lse[(static_cast<long long>(bh) * p.L1 + i) * p.L2 + j] = m_safe + log2f(l_new);
+            p.lse[(static_cast<long long>(bh) * p.L1 + i) * p.L2 + j] = m_safe * kLog2e + log2f(l_new);
         }
       }
     }
@@ -354,7 +433,7 @@ int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   p.so_h = a.so[1];
   p.so_i = a.so[2];
   p.so_j = a.so[3];
-  p.c1 = a.sm_scale * kLog2e;
+  p.scale = a.sm_scale;
   dim3 grid(a.L2 / 128, (a.L1 + C::G - 1) / C::G, a.B * a.H);
   kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmBias, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
@@ -366,6 +445,12 @@ int launch_fwd(const FwdArgs& a, cudaStream_t stream) {
   if (a.D == 32) return a.bf16 ? launch_fwd_t<32, true>(a, stream) : launch_fwd_t<32, false>(a, stream);
   return a.bf16 ? launch_fwd_t<64, true>(a, stream) : launch_fwd_t<64, false>(a, stream);
 }
+
+#ifdef FTA_TRACE
+int trace_read_fwd(unsigned long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 int fwd_rows_per_cta(int D) { return D == 32 ? FwdCfg<32>::G : FwdCfg<64>::G; }
 
