@@ -151,7 +151,8 @@ size_t fta_bwd_workspace_bytes(const FtaProblem* prob) {
   if (check_problem(prob)) return 0;
   const size_t rows = static_cast<size_t>(prob->B) * prob->H * prob->L1 * prob->L2;
   const size_t plane = static_cast<size_t>(prob->B) * prob->H * prob->L2 * prob->L2 * sizeof(float);
-  return align256(rows * prob->D * sizeof(float)) + align256(plane * fta_bwd_num_planes(prob));
+  return align256(rows * prob->D * sizeof(float)) + align256(plane * fta_bwd_num_planes(prob)) +
+         align256(plane / 2);  // + key-major copy of the bias (16-bit)
 }
 
 int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k, const FtaTensor5* v,
@@ -173,11 +174,19 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
   const long long plane_elems = static_cast<long long>(prob->B) * prob->H * prob->L2 * prob->L2;
   float* dq32 = static_cast<float*>(workspace);
   float* planes = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + align256(dq_bytes));
+  const int nplanes = fta_bwd_num_planes(prob);
+  void* bias_t = reinterpret_cast<uint8_t*>(planes) + align256(static_cast<size_t>(plane_elems) * 4 * nplanes);
   const bool bf16 = prob->dtype == FTA_BF16;
 
   fta::BwdArgs a;
+  FtaTensor4 bt;  // key-major copy: (B, H, key, query) contiguous
+  bt.ptr = bias_t;
+  bt.stride[0] = static_cast<int64_t>(prob->H) * prob->L2 * prob->L2;
+  bt.stride[1] = static_cast<int64_t>(prob->L2) * prob->L2;
+  bt.stride[2] = prob->L2;
+  bt.stride[3] = 1;
   if ((rc = map5(&a.tmQ, prob, q)) || (rc = map5(&a.tmK, prob, k)) || (rc = map5(&a.tmV, prob, v)) ||
-      (rc = map5(&a.tmDO, prob, dout)) || (rc = map_bias(&a.tmBias, prob, bias, 128, 0)))
+      (rc = map5(&a.tmDO, prob, dout)) || (rc = map_bias(&a.tmBiasT, prob, &bt, 64, 128)))
     return rc;
   a.lse = lse;
   a.delta = delta;
@@ -202,12 +211,15 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
 
   cudaError_t e = cudaMemsetAsync(dq32, 0, dq_bytes, st);
   if (e != cudaSuccess) return cuda_fail(e);
+  long long sb[4];
+  for (int i = 0; i < 4; ++i) sb[i] = bias->stride[i];
+  if (fta::launch_transpose_bias(bias->ptr, sb, bias_t, prob->B, prob->H, prob->L2, st) != 0)
+    return cuda_fail(cudaGetLastError());
   if (fta::launch_bwd(a, st) != 0) return cuda_fail(cudaGetLastError());
   if (fta::launch_dq_finalize(dq32, dq->ptr, sdq, prob->B, prob->H, prob->L1, prob->L2, prob->D, sm_scale, bf16,
                               st) != 0)
     return cuda_fail(cudaGetLastError());
-  if (fta::launch_dbias_finalize(planes, fta_bwd_num_planes(prob), plane_elems, dbias_f32, dbias_cast, bf16,
-                                 st) != 0)
+  if (fta::launch_dbias_finalize(planes, nplanes, plane_elems, dbias_f32, dbias_cast, bf16, st) != 0)
     return cuda_fail(cudaGetLastError());
   return FTA_OK;
 }

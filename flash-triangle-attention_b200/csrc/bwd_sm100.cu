@@ -14,7 +14,8 @@
 //
 // The tile is split in two 64-query halves, one per compute warpgroup, each with its own
 // S^T / dP^T columns and barriers, so the tensor core works on one half while the CUDA cores
-// work on the other.
+// work on the other. The bias is read from a transposed copy (key-major) so that the thread
+// that owns a key row reads its 64 query columns with 16-byte shared-memory loads.
 //
 // dBias: each thread owns one key column and 64 query rows of the (jb,kb) tile and sums dS
 // (float32, before rounding) over the G rows in registers; the sums are then added to the
@@ -26,6 +27,7 @@
 //   warps 0-3 : compute warpgroup 0 (queries 0..63 of the tile)   also stores dV
 //   warps 4-7 : compute warpgroup 1 (queries 64..127)             also reduces dQ, stores dK
 //   warp 8    : TMA producer      warp 9 : tcgen05 issuer      warps 10-11 : idle
+// Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
 #include "fta_kernels.h"
 #include "tc05.cuh"
 
@@ -48,7 +50,7 @@ __device__ unsigned long long g_trace_bwd[8192];
 
 template <int kD>
 struct BwdCfg {
-  static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + D + 2*D*G <= 512)
+  static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + 2*D + 2*D*G <= 512)
   static constexpr int NQ = (kD == 32) ? 4 : 2;  // Q/dO ring depth
   static constexpr int TILE_B = 128 * kD * 2;
   static constexpr int STAGE_B = 2 * TILE_B + 1024;  // Q, dO, lse[128], delta[128]
@@ -78,8 +80,8 @@ struct BwdCfg {
   // TMEM columns
   static constexpr uint32_t TM_ST = 0;
   static constexpr uint32_t TM_DP = 128;
-  static constexpr uint32_t TM_DQ = 256;
-  static constexpr uint32_t TM_ACC = 256 + kD;  // dK_g at TM_ACC + g*2*kD, dV_g right after
+  static constexpr uint32_t TM_DQ = 256;             // two dQ buffers of kD columns
+  static constexpr uint32_t TM_ACC = 256 + 2 * kD;   // dK_g at TM_ACC + g*2*kD, dV_g right after
   static_assert(TM_ACC + G * 2 * kD <= 512, "TMEM budget");
 };
 
@@ -112,18 +114,11 @@ __device__ __forceinline__ void red_add(float* addr, float a) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
 }
 
-template <bool kBf16>
-__device__ __forceinline__ float ld16_as_float(const uint8_t* p) {
-  const uint16_t v = *reinterpret_cast<const uint16_t*>(p);
-  if constexpr (kBf16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
-  else return __half2float(__ushort_as_half(v));
-}
-
 template <int kD, bool kBf16>
 __global__ void __launch_bounds__(384, 1)
 fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-               const __grid_constant__ CUtensorMap tmBias, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmBiasT, const BwdParams p) {
   using C = BwdCfg<kD>;
   constexpr int G = C::G;
   extern __shared__ uint8_t smem_raw[];
@@ -131,12 +126,13 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sKV = smem + C::OFF_KV;    // [g][K tile | V tile]
   uint8_t* sQDO = smem + C::OFF_QDO;  // [stage][Q | dO | lse | delta]
-  uint8_t* sBias = smem + C::OFF_BIAS;
+  uint8_t* sBias = smem + C::OFF_BIAS;  // [stage][query half][key row][64 queries], 128B swizzle
   uint8_t* sDS = smem + C::OFF_DS;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-  auto bar = [&](int i) { return smem_u32(&bars[i]); };
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = p.L2 / 128, nq = p.L2 / 128;
@@ -160,11 +156,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(bar(C::B_BIASFULL + i), 1);
       mbar_init(bar(C::B_BIASEMPTY + i), 8);
       mbar_init(bar(C::B_SFULL + i), 1);
-      mbar_init(bar(C::B_PFULL + i), 128);
+      mbar_init(bar(C::B_PFULL + i), 4);  // one arrive per warp of the warpgroup
     }
     mbar_init(bar(C::B_DQDONE), 1);
     mbar_init(bar(C::B_ACCFULL), 1);
-    mbar_init(bar(C::B_ACCFREE), 256);
+    mbar_init(bar(C::B_ACCFREE), 8);
     mbar_fence_init();
   }
   if (warp == 9) {
@@ -178,130 +174,147 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
   if (warp >= 8) {
     reg_dec<88>();
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
-      tma_prefetch_desc(&tmBias);
+    if (warp == 8) {
+      // ---------------------------------------------------------------- TMA producer
+      if (elect_one()) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmDO);
+        tma_prefetch_desc(&tmBiasT);
+      }
       bool ok = true;
       int tt = 0, nb = 0;
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = (r + n * p.NP) * G;
         const int Gc = min(G, p.L1 - i0);
-        ok = mbar_wait(bar(C::B_KVFREE), (n & 1) ^ 1, w, 0x21);
+        ok = mbar_wait_warp(bar(C::B_KVFREE), (n & 1) ^ 1, w, 0x21);
         if (!ok) break;
-        mbar_expect_tx(bar(C::B_KVFULL), Gc * 2 * C::TILE_B);
-        for (int g = 0; g < Gc; ++g) {
-          tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL), 0, kb * 128, i0 + g, h, b);
-          tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL), 0, kb * 128,
-                      i0 + g, h, b);
+        if (elect_one()) {
+          mbar_expect_tx(bar(C::B_KVFULL), Gc * 2 * C::TILE_B);
+          for (int g = 0; g < Gc; ++g) {
+            tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL), 0, kb * 128, i0 + g, h, b);
+            tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL), 0, kb * 128,
+                        i0 + g, h, b);
+          }
         }
         for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
           const int bs = nb & 1;
-          ok = mbar_wait(bar(C::B_BIASEMPTY + bs), ((nb >> 1) & 1) ^ 1, w, 0x22);
+          ok = mbar_wait_warp(bar(C::B_BIASEMPTY + bs), ((nb >> 1) & 1) ^ 1, w, 0x22);
           if (!ok) break;
-          mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
-          tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128, jb * 128,
-                      h, b);
+          if (elect_one()) {
+            // transposed bias: innermost coordinate = query, then key
+            mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
+            tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBiasT, bar(C::B_BIASFULL + bs), jb * 128,
+                        kb * 128, h, b);
+            tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBiasT, bar(C::B_BIASFULL + bs),
+                        jb * 128 + 64, kb * 128, h, b);
+          }
           for (int g = 0; g < Gc; ++g, ++tt) {
             const int s = tt % C::NQ;
-            ok = mbar_wait(bar(C::B_QDOEMPTY + s), ((tt / C::NQ) & 1) ^ 1, w, 0x23);
+            ok = mbar_wait_warp(bar(C::B_QDOEMPTY + s), ((tt / C::NQ) & 1) ^ 1, w, 0x23);
             if (!ok) break;
-            uint8_t* st = sQDO + s * C::STAGE_B;
-            mbar_expect_tx(bar(C::B_QDOFULL + s), C::STAGE_B);
-            tma_load_5d(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
-            tma_load_5d(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
-            const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
-            bulk_load_1d(smem_u32(st + 2 * C::TILE_B), p.lse + roff, 512, bar(C::B_QDOFULL + s));
-            bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.delta + roff, 512, bar(C::B_QDOFULL + s));
+            if (elect_one()) {
+              uint8_t* st = sQDO + s * C::STAGE_B;
+              mbar_expect_tx(bar(C::B_QDOFULL + s), C::STAGE_B);
+              tma_load_5d(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
+              tma_load_5d(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
+              const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
+              bulk_load_1d(smem_u32(st + 2 * C::TILE_B), p.lse + roff, 512, bar(C::B_QDOFULL + s));
+              bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.delta + roff, 512, bar(C::B_QDOFULL + s));
+            }
           }
         }
       }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    } else if (warp == 9) {
+      // ---------------------------------------------------------------- MMA issuer
       constexpr int fmt = kBf16 ? 1 : 0;
       constexpr uint32_t idesc_s = umma_idesc_f16(fmt, 128, 64, 0, 0);    // S^T, dP^T halves
       constexpr uint32_t idesc_acc = umma_idesc_f16(fmt, 128, kD, 0, 1);  // dV, dK (A in TMEM, B M-major)
       constexpr uint32_t idesc_dq = umma_idesc_f16(fmt, 128, kD, 1, 1);   // dQ (A, B M-major)
+      const uint32_t sKV_a = smem_u32(sKV), sQDO_a = smem_u32(sQDO), sDS_a = smem_u32(sDS);
       bool ok = true;
       int tt = 0;
       // S^T_w / dP^T_w of the tile with ring index `tix`, row g of the group
       auto issue_sdp = [&](int tix, int g, int wh, bool wait_stage) -> bool {
         const int s = tix % C::NQ;
-        if (wait_stage && !mbar_wait(bar(C::B_QDOFULL + s), (tix / C::NQ) & 1, w, 0x31)) return false;
+        if (wait_stage && !mbar_wait_warp(bar(C::B_QDOFULL + s), (tix / C::NQ) & 1, w, 0x31)) return false;
         tc_fence_after_sync();
-        const uint8_t* st = sQDO + s * C::STAGE_B;
-        const uint64_t dK = umma_smem_desc(smem_u32(sKV + g * 2 * C::TILE_B), 16, C::SBO, C::SWZ);
-        const uint64_t dV = umma_smem_desc(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), 16, C::SBO, C::SWZ);
-        const uint64_t dQ = umma_smem_desc(smem_u32(st + wh * 64 * C::ROW_B), 16, C::SBO, C::SWZ);
-        const uint64_t dO = umma_smem_desc(smem_u32(st + C::TILE_B + wh * 64 * C::ROW_B), 16, C::SBO, C::SWZ);
+        const uint32_t st = sQDO_a + s * C::STAGE_B;
+        const uint64_t dK = umma_smem_desc(sKV_a + g * 2 * C::TILE_B, 16, C::SBO, C::SWZ);
+        const uint64_t dV = umma_smem_desc(sKV_a + g * 2 * C::TILE_B + C::TILE_B, 16, C::SBO, C::SWZ);
+        const uint64_t dQ = umma_smem_desc(st + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
+        const uint64_t dO = umma_smem_desc(st + C::TILE_B + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks)
-          umma_ss(tbase + C::TM_ST + wh * 64, dK + ks * 2, dQ + ks * 2, idesc_s, ks > 0);
+          for (int ks = 0; ks < kD / 16; ++ks)
+            umma_ss(tbase + C::TM_ST + wh * 64, dK + ks * 2, dQ + ks * 2, idesc_s, ks > 0);
 #pragma unroll
-        for (int ks = 0; ks < kD / 16; ++ks)
-          umma_ss(tbase + C::TM_DP + wh * 64, dV + ks * 2, dO + ks * 2, idesc_s, ks > 0);
-        umma_commit(bar(C::B_SFULL + wh));
+          for (int ks = 0; ks < kD / 16; ++ks)
+            umma_ss(tbase + C::TM_DP + wh * 64, dV + ks * 2, dO + ks * 2, idesc_s, ks > 0);
+          umma_commit(bar(C::B_SFULL + wh));
+        }
+        __syncwarp();
         return true;
       };
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = (r + n * p.NP) * G;
         const int Gc = min(G, p.L1 - i0);
         const int T = nq * Gc;
-        ok = mbar_wait(bar(C::B_KVFULL), n & 1, w, 0x32);
+        ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32);
         if (!ok) break;
         ok = issue_sdp(tt, 0, 0, true) && issue_sdp(tt, 0, 1, false);
         for (int t = 0; t < T && ok; ++t, ++tt) {
           const int jb = t / Gc, g = t % Gc, s = tt % C::NQ;
-          const uint8_t* st = sQDO + s * C::STAGE_B;
+          const uint32_t st = sQDO_a + s * C::STAGE_B;
           for (int wh = 0; wh < 2 && ok; ++wh) {
             FTA_STAMP(2, wh * 3 + 0, tt);
-            ok = mbar_wait(bar(C::B_PFULL + wh), tt & 1, w, 0x33);
+            ok = mbar_wait_warp(bar(C::B_PFULL + wh), tt & 1, w, 0x33);
             if (!ok) break;
             FTA_STAMP(2, wh * 3 + 1, tt);
             if (t == 0 && wh == 0 && n > 0) {
-              ok = mbar_wait(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
+              ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
               if (!ok) break;
             }
             tc_fence_after_sync();
-            const uint64_t dOm =
-                umma_smem_desc(smem_u32(st + C::TILE_B + wh * 64 * C::ROW_B), C::SBO, C::SBO, C::SWZ);
-            const uint64_t dQm = umma_smem_desc(smem_u32(st + wh * 64 * C::ROW_B), C::SBO, C::SBO, C::SWZ);
+            const uint64_t dOm = umma_smem_desc(st + C::TILE_B + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
+            const uint64_t dQm = umma_smem_desc(st + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
             const uint32_t tdk = tbase + C::TM_ACC + g * 2 * kD, tdv = tdk + kD;
+            const uint32_t acc_first = (jb > 0 || wh > 0) ? 1u : 0u;
+            if (elect_one()) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_ts(tdv, tbase + C::TM_ST + wh * 64 + ks * 8, dOm + ks * ((2 * C::SBO) >> 4), idesc_acc,
-                      (jb > 0 || wh > 0 || ks > 0) ? 1u : 0u);
+              for (int ks = 0; ks < 4; ++ks)
+                umma_ts(tdv, tbase + C::TM_ST + wh * 64 + ks * 8, dOm + ks * ((2 * C::SBO) >> 4), idesc_acc,
+                        ks > 0 ? 1u : acc_first);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_ts(tdk, tbase + C::TM_DP + wh * 64 + ks * 8, dQm + ks * ((2 * C::SBO) >> 4), idesc_acc,
-                      (jb > 0 || wh > 0 || ks > 0) ? 1u : 0u);
-            if (wh == 1) {
-              const uint64_t dSm = umma_smem_desc(smem_u32(sDS), 16384, 1024, kSwz128);
-              const uint64_t dKm = umma_smem_desc(smem_u32(sKV + g * 2 * C::TILE_B), C::SBO, C::SBO, C::SWZ);
+              for (int ks = 0; ks < 4; ++ks)
+                umma_ts(tdk, tbase + C::TM_DP + wh * 64 + ks * 8, dQm + ks * ((2 * C::SBO) >> 4), idesc_acc,
+                        ks > 0 ? 1u : acc_first);
+              if (wh == 1) {
+                const uint64_t dSm = umma_smem_desc(sDS_a, 16384, 1024, kSwz128);
+                const uint64_t dKm = umma_smem_desc(sKV_a + g * 2 * C::TILE_B, C::SBO, C::SBO, C::SWZ);
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks)
-                umma_ss(tbase + C::TM_DQ, dSm + ks * (2048 >> 4), dKm + ks * ((2 * C::SBO) >> 4), idesc_dq,
-                        ks > 0);
-              umma_commit(bar(C::B_QDOEMPTY + s));
-              umma_commit(bar(C::B_DQDONE));
+                for (int ks = 0; ks < 8; ++ks)
+                  umma_ss(tbase + C::TM_DQ + (tt & 1) * kD, dSm + ks * (2048 >> 4),
+                          dKm + ks * ((2 * C::SBO) >> 4), idesc_dq, ks > 0);
+                umma_commit(bar(C::B_QDOEMPTY + s));
+                umma_commit(bar(C::B_DQDONE));
+              }
             }
+            __syncwarp();
             if (t + 1 < T) ok = issue_sdp(tt + 1, (t + 1) % Gc, wh, wh == 0);
             FTA_STAMP(2, wh * 3 + 2, tt);
           }
         }
         if (ok) {
-          umma_commit(bar(C::B_ACCFULL));
-          umma_commit(bar(C::B_KVFREE));
+          if (elect_one()) {
+            umma_commit(bar(C::B_ACCFULL));
+            umma_commit(bar(C::B_KVFREE));
+          }
+          __syncwarp();
         }
       }
     }
-  }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
     reg_inc<208>();
@@ -311,91 +324,108 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tST = tbase + C::TM_ST + wh * 64 + lane_off;
     const uint32_t tDP = tbase + C::TM_DP + wh * 64 + lane_off;
     float* plane = p.planes + (static_cast<long long>(r) * p.BH + bh) * p.L2 * p.L2;
+    const f32x2 nc1_2 = mk2(-p.c1, -p.c1);
+    const f32x2 nlog2e2 = mk2(-kLog2e, -kLog2e);
+    const f32x2 neg1_2 = mk2(-1.f, -1.f);
     bool ok = true;
     int tt = 0, nb = 0;
+    // reduce one finished dQ tile (TMEM buffer `buf`) into the float32 dQ accumulator
+    auto reduce_dq = [&](int buf, int irow, int jblk) {
+      float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128 + key) * kD;
+#pragma unroll
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t qv[32];
+        tmem_ld32(tbase + C::TM_DQ + buf * kD + c * 32 + lane_off, qv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          red_add_v4(dst + c * 32 + j * 4, __uint_as_float(qv[4 * j]), __uint_as_float(qv[4 * j + 1]),
+                     __uint_as_float(qv[4 * j + 2]), __uint_as_float(qv[4 * j + 3]));
+      }
+    };
     for (int n = 0; n < ngroups && ok; ++n) {
       const int i0 = (r + n * p.NP) * G;
       const int Gc = min(G, p.L1 - i0);
       for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
-        float acc[64];
+        f32x2 acc[32];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) acc[c] = 0.f;
+        for (int c = 0; c < 32; ++c) acc[c] = mk2(0.f, 0.f);
         const int bs = nb & 1;
         ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
         if (!ok) break;
-        const uint8_t* bcol = sBias + bs * C::BIAS_B + (wh * 64) * 256 + key * 2;
+        const uint8_t* brow = sBias + bs * C::BIAS_B + wh * 16384 + key * 128;
         for (int g = 0; g < Gc; ++g, ++tt) {
           const int s = tt % C::NQ;
           const uint8_t* st = sQDO + s * C::STAGE_B;
           if ((warp & 3) == 0) FTA_STAMP(wh, 0, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
-          if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // lse / delta visible
           if (!ok) break;
+          if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
           tc_fence_after_sync();
-          if (wh == 1 && !(jb == 0 && g == 0)) {
-            // dQ of the previous tile of this group is complete: reduce it into the fp32 buffer
-            const int pt = jb * Gc + g - 1;
-            const int pjb = pt / Gc, pg = pt % Gc;
-            float* dst = p.dq32 +
-                         ((static_cast<long long>(bh) * p.L1 + i0 + pg) * p.L2 + pjb * 128 + key) * kD;
-#pragma unroll
-            for (int c = 0; c < kD / 32; ++c) {
-              uint32_t qv[32];
-              tmem_ld32(tbase + C::TM_DQ + c * 32 + lane_off, qv);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                red_add_v4(dst + c * 32 + j * 4, __uint_as_float(qv[4 * j]), __uint_as_float(qv[4 * j + 1]),
-                           __uint_as_float(qv[4 * j + 2]), __uint_as_float(qv[4 * j + 3]));
-            }
-          }
-          if (tt > 0) {  // dS staging buffer free again (the previous dQ MMA has read it)
-            ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
-            if (!ok) break;
-          }
-          if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
-          const float* lse_s = reinterpret_cast<const float*>(st + 2 * C::TILE_B) + wh * 64;
-          const float* del_s = reinterpret_cast<const float*>(st + 2 * C::TILE_B + 512) + wh * 64;
+          const float4* lse4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + wh * 16;
+          const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + wh * 16;
+          uint32_t dd[32];  // dS^T of this key row, 64 queries, packed 16-bit pairs
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
             uint32_t sv[32], dv[32];
             tmem_ld32(tST + cc * 32, sv);
             tmem_ld32(tDP + cc * 32, dv);
             tmem_ld_wait();
-            uint32_t pp[16], dd[16];
+            uint32_t pp[16];
 #pragma unroll
-            for (int c2 = 0; c2 < 16; ++c2) {
-              const int q0 = cc * 32 + 2 * c2;
-              const float2 ls = *reinterpret_cast<const float2*>(lse_s + q0);
-              const float2 de = *reinterpret_cast<const float2*>(del_s + q0);
-              const float b0 = ld16_as_float<kBf16>(bcol + q0 * 256);
-              const float b1 = ld16_as_float<kBf16>(bcol + (q0 + 1) * 256);
-              const float x0 = fmaf(__uint_as_float(sv[2 * c2]), p.c1, fmaf(b0, kLog2e, -ls.x));
-              const float x1 = fmaf(__uint_as_float(sv[2 * c2 + 1]), p.c1, fmaf(b1, kLog2e, -ls.y));
-              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-              const float ds0 = p0 * (__uint_as_float(dv[2 * c2]) - de.x);
-              const float ds1 = p1 * (__uint_as_float(dv[2 * c2 + 1]) - de.y);
-              acc[q0] += ds0;
-              acc[q0 + 1] += ds1;
-              pp[c2] = pack2<kBf16>(p0, p1);
-              dd[c2] = pack2<kBf16>(ds0, ds1);
+            for (int c8 = 0; c8 < 4; ++c8) {
+              const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((cc * 4 + c8) ^ (key & 7)) << 4));
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+              const float4 la = lse4[cc * 8 + c8 * 2], lb = lse4[cc * 8 + c8 * 2 + 1];
+              const float4 da = del4[cc * 8 + c8 * 2], db = del4[cc * 8 + c8 * 2 + 1];
+              const f32x2 lse2[4] = {mk2(la.x, la.y), mk2(la.z, la.w), mk2(lb.x, lb.y), mk2(lb.z, lb.w)};
+              const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int idx = c8 * 8 + 2 * e;  // column within the 32-column chunk
+                float b0, b1, nx0, nx1, ds0, ds1;
+                unpack2<kBf16>(bw[e], b0, b1);
+                // -x = -(s*c1 + b*log2e - lse)
+                const f32x2 nx = fma2(mk2(__uint_as_float(sv[idx]), __uint_as_float(sv[idx + 1])), nc1_2,
+                                      fma2(mk2(b0, b1), nlog2e2, lse2[e]));
+                un2(nx, nx0, nx1);
+                const float p0 = fast_exp2(-nx0), p1 = fast_exp2(-nx1);
+                const f32x2 u = fma2(del2[e], neg1_2, mk2(__uint_as_float(dv[idx]), __uint_as_float(dv[idx + 1])));
+                const f32x2 ds = mul2(mk2(p0, p1), u);
+                acc[cc * 16 + c8 * 4 + e] = add2(acc[cc * 16 + c8 * 4 + e], ds);
+                un2(ds, ds0, ds1);
+                pp[c8 * 4 + e] = pack2<kBf16>(p0, p1);
+                dd[cc * 16 + c8 * 4 + e] = pack2<kBf16>(ds0, ds1);
+              }
             }
             tmem_st16(tST + cc * 16, pp);
-            tmem_st16(tDP + cc * 16, dd);
-            // dS^T row of this key into the M-major staging tile (128-byte swizzle)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 v4 = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
-              *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + (((cc * 4 + j) ^ (key & 7)) << 4)) = v4;
-            }
+            tmem_st16(tDP + cc * 16, dd + cc * 16);
           }
-          if ((warp & 3) == 0) FTA_STAMP(wh, 3, tt);
+          if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
+          if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
+            ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
+            if (!ok) break;
+          }
+          // dS^T row of this key into the M-major staging tile (128-byte swizzle)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 v4 = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
+            *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + ((j ^ (key & 7)) << 4)) = v4;
+          }
           tmem_st_wait();
           fence_proxy_async_smem();
           tc_fence_before_sync();
-          mbar_arrive(bar(C::B_PFULL + wh));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::B_PFULL + wh));
+          if ((warp & 3) == 0) FTA_STAMP(wh, 3, tt);
+          if (wh == 1 && !(jb == 0 && g == 0)) {
+            // dQ of the previous tile of this group is complete (DQDONE waited above)
+            const int pt = jb * Gc + g - 1;
+            tc_fence_after_sync();
+            reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+          }
           if ((warp & 3) == 0) FTA_STAMP(wh, 4, tt);
         }
         if (!ok) break;
@@ -406,10 +436,20 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         float* dst = plane + (static_cast<long long>(jb) * 128 + wh * 64) * p.L2 + kb * 128 + key;
         if (n == 0) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) dst[static_cast<long long>(c) * p.L2] = acc[c];
+          for (int c = 0; c < 32; ++c) {
+            float a0, a1;
+            un2(acc[c], a0, a1);
+            dst[static_cast<long long>(2 * c) * p.L2] = a0;
+            dst[static_cast<long long>(2 * c + 1) * p.L2] = a1;
+          }
         } else {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) red_add(dst + static_cast<long long>(c) * p.L2, acc[c]);
+          for (int c = 0; c < 32; ++c) {
+            float a0, a1;
+            un2(acc[c], a0, a1);
+            red_add(dst + static_cast<long long>(2 * c) * p.L2, a0);
+            red_add(dst + static_cast<long long>(2 * c + 1) * p.L2, a1);
+          }
         }
       }
       if (!ok) break;
@@ -419,18 +459,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tc_fence_after_sync();
       if (wh == 1) {
         const int pt = nq * Gc - 1;
-        const int pjb = pt / Gc, pg = pt % Gc;
-        float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + i0 + pg) * p.L2 + pjb * 128 + key) * kD;
-#pragma unroll
-        for (int c = 0; c < kD / 32; ++c) {
-          uint32_t qv[32];
-          tmem_ld32(tbase + C::TM_DQ + c * 32 + lane_off, qv);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            red_add_v4(dst + c * 32 + j * 4, __uint_as_float(qv[4 * j]), __uint_as_float(qv[4 * j + 1]),
-                       __uint_as_float(qv[4 * j + 2]), __uint_as_float(qv[4 * j + 3]));
-        }
+        reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
       }
       {
         // warpgroup 0 stores dV, warpgroup 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518)
@@ -459,7 +488,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
       tc_fence_before_sync();
-      mbar_arrive(bar(C::B_ACCFREE));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::B_ACCFREE));
     }
   }
 
@@ -500,7 +530,7 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   p.c1 = a.sm_scale * kLog2e;
   p.scale = a.sm_scale;
   const int grid = a.B * a.H * NP * (a.L2 / 128);
-  kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBias, p);
+  kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -21,7 +21,7 @@ int launch_fwd(const FwdArgs& a, cudaStream_t stream);
 int fwd_rows_per_cta(int D);
 
 struct BwdArgs {
-  CUtensorMap tmQ, tmK, tmV, tmDO, tmBias;
+  CUtensorMap tmQ, tmK, tmV, tmDO, tmBiasT;  // tmBiasT: over the key-major copy of the bias
   const float* lse;    // (B,H,L1,L2)
   const float* delta;  // (B,H,L1,L2)
   float* dq32;         // (B,H,L1,L2,D) float32, zeroed; receives sum over key blocks of dS K
@@ -42,6 +42,10 @@ int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms);
 int launch_preprocess(const void* o, const long long so[4], const void* dout, const long long sdo[4],
                       float* delta, int B, int H, int L1, int L2, int D, bool bf16,
                       cudaStream_t stream);
+
+// out[bh][k][q] = bias[b][h][q][k] (16-bit elements); `sb` = element strides of the bias
+int launch_transpose_bias(const void* bias, const long long sb[4], void* out, int B, int H, int L2,
+                          cudaStream_t stream);
 
 // out_f32[e] = sum_p planes[p][e] (fixed order), optional rounded copy
 int launch_dbias_finalize(const float* planes, int nplanes, long long plane_elems, float* out_f32,

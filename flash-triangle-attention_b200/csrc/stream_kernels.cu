@@ -5,6 +5,7 @@
 //                   flash_tt_attn.py:266-288)
 //  dbias_finalize : dBias[e] = sum over partial planes, in plane order, plus the rounded copy
 //                   (replaces the fp16 atomics into a zeroed buffer, flash_tt_attn.py:425-426, 613)
+//  transpose_bias : key-major copy of the pair bias for the backward kernel
 //  dq_finalize    : dQ = (dtype)(sm_scale * dQ_f32)             (the scaling of flash_tt_attn.py:430, 549)
 #include "fta_kernels.h"
 #include "tc05.cuh"
@@ -122,6 +123,35 @@ __global__ void __launch_bounds__(256) dq_finalize_kernel(const float* __restric
   }
 }
 
+// out[bh][k][q] = in[b][h][q][k] for 16-bit elements, 64 x 64 tiles staged in shared memory.
+__global__ void __launch_bounds__(256) transpose_bias_kernel(const uint16_t* __restrict__ in,
+                                                             uint16_t* __restrict__ out, int H, int L2,
+                                                             long long s_b, long long s_h, long long s_q) {
+  __shared__ uint16_t tile[64][66];
+  const int tiles = L2 / 64;
+  const int bh = blockIdx.y;
+  const int b = bh / H, h = bh % H;
+  const uint16_t* src = in + b * s_b + h * s_h;
+  uint16_t* dst = out + static_cast<long long>(bh) * L2 * L2;
+  for (int t = blockIdx.x; t < tiles * tiles; t += gridDim.x) {
+    const int q0 = (t / tiles) * 64, k0 = (t % tiles) * 64;
+    // 256 threads: 4 rows x 64 columns per pass; two 16-bit elements per thread
+    for (int i = threadIdx.x; i < 64 * 32; i += 256) {
+      const int rr = i / 32, c2 = (i % 32) * 2;
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(src + (q0 + rr) * s_q + k0 + c2);
+      tile[rr][c2] = static_cast<uint16_t>(v & 0xffffu);
+      tile[rr][c2 + 1] = static_cast<uint16_t>(v >> 16);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 64 * 32; i += 256) {
+      const int rr = i / 32, c2 = (i % 32) * 2;  // rr = key row of the output, c2 = query column
+      const uint32_t v = static_cast<uint32_t>(tile[c2][rr]) | (static_cast<uint32_t>(tile[c2 + 1][rr]) << 16);
+      *reinterpret_cast<uint32_t*>(dst + static_cast<long long>(k0 + rr) * L2 + q0 + c2) = v;
+    }
+    __syncthreads();
+  }
+}
+
 int grid_for(long long work_items, int threads) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -152,6 +182,15 @@ int launch_preprocess(const void* o, const long long so[4], const void* dout, co
     if (bf16) FTA_PRE(64, true); else FTA_PRE(64, false);
   }
 #undef FTA_PRE
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int launch_transpose_bias(const void* bias, const long long sb[4], void* out, int B, int H, int L2,
+                          cudaStream_t stream) {
+  const int tiles = (L2 / 64) * (L2 / 64);
+  dim3 grid(tiles < 1024 ? tiles : 1024, B * H);
+  transpose_bias_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(bias),
+                                                  static_cast<uint16_t*>(out), H, L2, sb[0], sb[1], sb[2]);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
