@@ -8,7 +8,7 @@
 // (outer) and the G rows (inner):
 //
 //   S^T  = K Q^T, dP^T = V dO^T                       (tcgen05, operands in smem)
-//   P^T  = exp2(S^T*c1 + bias^T*log2e - lse),  dS^T = P^T * (dP^T - delta)   (CUDA cores)
+//   P^T  = exp2((S^T*scale + bias^T - max)*log2e - log2 sum),  dS^T = P^T * (dP^T - delta)   (CUDA cores)
 //   dV  += P^T dO, dK += dS^T Q                        (A operand read from TMEM)
 //   dQ   = dS K                                        (dS staged in smem, M-major)
 //
@@ -53,7 +53,7 @@ struct BwdCfg {
   static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + 2*D + 2*D*G <= 512)
   static constexpr int NQ = (kD == 32) ? 4 : 2;  // Q/dO ring depth
   static constexpr int TILE_B = 128 * kD * 2;
-  static constexpr int STAGE_B = 2 * TILE_B + 1024;  // Q, dO, lse[128], delta[128]
+  static constexpr int STAGE_B = 2 * TILE_B + 2048;  // Q, dO, -max[128], -log2sum[128], delta[128], pad
   static constexpr int BIAS_B = 128 * 128 * 2;
   static constexpr int DS_B = 128 * 128 * 2;
   static constexpr int OFF_KV = 0;
@@ -86,7 +86,7 @@ struct BwdCfg {
 };
 
 struct BwdParams {
-  const float* lse;
+  const float* lse;  // two planes: -max (natural-log units), -log2(sum)
   const float* delta;
   float* dq32;
   void* dk;
@@ -95,8 +95,8 @@ struct BwdParams {
   int* status;
   int H, L1, L2, NP, BH;
   long long sdk[4], sdv[4];
-  float c1;     // sm_scale * log2(e)
   float scale;  // sm_scale
+  long long stat_stride;  // elements between the two statistics planes
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -216,12 +216,14 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (!ok) break;
             if (elect_one()) {
               uint8_t* st = sQDO + s * C::STAGE_B;
-              mbar_expect_tx(bar(C::B_QDOFULL + s), C::STAGE_B);
+              mbar_expect_tx(bar(C::B_QDOFULL + s), 2 * C::TILE_B + 1536);
               tma_load_5d(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
               tma_load_5d(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
               const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B), p.lse + roff, 512, bar(C::B_QDOFULL + s));
-              bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.delta + roff, 512, bar(C::B_QDOFULL + s));
+              bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.lse + p.stat_stride + roff, 512,
+                           bar(C::B_QDOFULL + s));
+              bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 1024), p.delta + roff, 512, bar(C::B_QDOFULL + s));
             }
           }
         }
@@ -324,8 +326,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tST = tbase + C::TM_ST + wh * 64 + lane_off;
     const uint32_t tDP = tbase + C::TM_DP + wh * 64 + lane_off;
     float* plane = p.planes + (static_cast<long long>(r) * p.BH + bh) * p.L2 * p.L2;
-    const f32x2 nc1_2 = mk2(-p.c1, -p.c1);
-    const f32x2 nlog2e2 = mk2(-kLog2e, -kLog2e);
+    const f32x2 scale2 = mk2(p.scale, p.scale);
+    const f32x2 log2e2 = mk2(kLog2e, kLog2e);
     const f32x2 neg1_2 = mk2(-1.f, -1.f);
     bool ok = true;
     int tt = 0, nb = 0;
@@ -364,8 +366,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!ok) break;
           if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
           tc_fence_after_sync();
-          const float4* lse4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + wh * 16;
-          const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + wh * 16;
+          const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + wh * 16;
+          const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + wh * 16;
+          const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1024) + wh * 16;
           uint32_t dd[32];  // dS^T of this key row, 64 queries, packed 16-bit pairs
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
@@ -378,20 +381,23 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int c8 = 0; c8 < 4; ++c8) {
               const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((cc * 4 + c8) ^ (key & 7)) << 4));
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-              const float4 la = lse4[cc * 8 + c8 * 2], lb = lse4[cc * 8 + c8 * 2 + 1];
+              const float4 ma = nm4[cc * 8 + c8 * 2], mb = nm4[cc * 8 + c8 * 2 + 1];
+              const float4 la = nl4[cc * 8 + c8 * 2], lb = nl4[cc * 8 + c8 * 2 + 1];
               const float4 da = del4[cc * 8 + c8 * 2], db = del4[cc * 8 + c8 * 2 + 1];
-              const f32x2 lse2[4] = {mk2(la.x, la.y), mk2(la.z, la.w), mk2(lb.x, lb.y), mk2(lb.z, lb.w)};
+              const f32x2 nm2[4] = {mk2(ma.x, ma.y), mk2(ma.z, ma.w), mk2(mb.x, mb.y), mk2(mb.z, mb.w)};
+              const f32x2 nl2[4] = {mk2(la.x, la.y), mk2(la.z, la.w), mk2(lb.x, lb.y), mk2(lb.z, lb.w)};
               const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int idx = c8 * 8 + 2 * e;  // column within the 32-column chunk
-                float b0, b1, nx0, nx1, ds0, ds1;
+                float b0, b1, y0, y1, ds0, ds1;
                 unpack2<kBf16>(bw[e], b0, b1);
-                // -x = -(s*c1 + b*log2e - lse)
-                const f32x2 nx = fma2(mk2(__uint_as_float(sv[idx]), __uint_as_float(sv[idx + 1])), nc1_2,
-                                      fma2(mk2(b0, b1), nlog2e2, lse2[e]));
-                un2(nx, nx0, nx1);
-                const float p0 = fast_exp2(-nx0), p1 = fast_exp2(-nx1);
+                // x = s*scale + b exactly as the forward pass formed it; (x - max) is then exact
+                // for x near the max whatever its magnitude; y = (x - max)*log2e - log2(sum)
+                const f32x2 x = fma2(mk2(__uint_as_float(sv[idx]), __uint_as_float(sv[idx + 1])), scale2,
+                                     mk2(b0, b1));
+                un2(fma2(add2(x, nm2[e]), log2e2, nl2[e]), y0, y1);
+                const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
                 const f32x2 u = fma2(del2[e], neg1_2, mk2(__uint_as_float(dv[idx]), __uint_as_float(dv[idx + 1])));
                 const f32x2 ds = mul2(mk2(p0, p1), u);
                 acc[cc * 16 + c8 * 4 + e] = add2(acc[cc * 16 + c8 * 4 + e], ds);
@@ -527,8 +533,8 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
     p.sdk[i] = a.sdk[i];
     p.sdv[i] = a.sdv[i];
   }
-  p.c1 = a.sm_scale * kLog2e;
   p.scale = a.sm_scale;
+  p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
   const int grid = a.B * a.H * NP * (a.L2 / 128);
   kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;

@@ -22,7 +22,7 @@ int fwd_rows_per_cta(int D);
 
 struct BwdArgs {
   CUtensorMap tmQ, tmK, tmV, tmDO, tmBiasT;  // tmBiasT: over the key-major copy of the bias
-  const float* lse;    // (B,H,L1,L2)
+  const float* lse;    // (2,B,H,L1,L2): -max, -log2(sum)
   const float* delta;  // (B,H,L1,L2)
   float* dq32;         // (B,H,L1,L2,D) float32, zeroed; receives sum over key blocks of dS K
   void* dk;

@@ -1,5 +1,5 @@
 // Forward triangle attention for sm_100a: O = softmax(sm_scale * q k^T + bias) v and the
-// base-2 log-sum-exp, the work of the reference's `_attn_fwd` (flash_tt_attn.py:128-264).
+// softmax statistics (row max and log2 of the row sum), the work of the reference's `_attn_fwd` (flash_tt_attn.py:128-264).
 //
 // One CTA owns a 128-query block `jb` of a group of up to G consecutive L1 rows of one
 // (b,h). It walks the key blocks once (outer loop) and, inside, the G rows (inner loop), so
@@ -81,6 +81,7 @@ struct FwdParams {
   int H, L1, L2;
   long long so_b, so_h, so_i, so_j;  // element strides of O (D stride is 1)
   float scale;                       // sm_scale
+  long long stat_stride;             // elements between the two statistics planes
 };
 
 template <int N>
@@ -339,8 +340,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         if ((warp & 3) == 0) FTA_STAMP(wg, 4, n);
         // pass 2: p = 2^((x - m) * log2e), row sum, pack, hand P to the tensor core through TMEM
-        const float nm = -m_safe * kLog2e;
-        const f32x2 nm2 = mk2(nm, nm);
+        const f32x2 nm2 = mk2(-m_safe, -m_safe);
         f32x2 sum2a = mk2(0.f, 0.f), sum2b = mk2(0.f, 0.f);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -348,7 +348,9 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float y0, y1;
-            un2(fma2(mk2(__uint_as_float(sr[c * 32 + 2 * j]), __uint_as_float(sr[c * 32 + 2 * j + 1])), log2e2, nm2),
+            // (x - m) first: exact when x is close to m, whatever their magnitude (masked rows)
+            un2(mul2(add2(mk2(__uint_as_float(sr[c * 32 + 2 * j]), __uint_as_float(sr[c * 32 + 2 * j + 1])), nm2),
+                     log2e2),
                 y0, y1);
             const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
             if (j & 1) sum2b = add2(sum2b, mk2(p0, p1));
@@ -397,8 +399,13 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               }
             }
           }
-          if (i < p.L1)
-            p.lse[(static_cast<long long>(bh) * p.L1 + i) * p.L2 + j] = m_safe * kLog2e + log2f(l_new);
+          if (i < p.L1) {
+            // softmax statistics for the backward pass: -max (natural-log units) and -log2(sum).
+            // Kept apart: their sum in one float would lose log2(sum) when |max| is huge.
+            const long long ridx = (static_cast<long long>(bh) * p.L1 + i) * p.L2 + j;
+            p.lse[ridx] = -m_safe;
+            p.lse[p.stat_stride + ridx] = -log2f(l_new);
+          }
         }
       }
     }
@@ -434,6 +441,7 @@ int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   p.so_i = a.so[2];
   p.so_j = a.so[3];
   p.scale = a.sm_scale;
+  p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
   dim3 grid(a.L2 / 128, (a.L1 + C::G - 1) / C::G, a.B * a.H);
   kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmBias, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;

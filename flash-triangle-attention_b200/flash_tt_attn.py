@@ -91,7 +91,7 @@ class _attention(torch.autograd.Function):
 
         q, k, v, b_pw = _dense(q), _dense(k), _dense(v), _dense(b_pw)
         o = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=q.device)
-        lse = torch.empty((B, H, L1, L2), dtype=torch.float32, device=q.device)
+        lse = torch.empty((2, B, H, L1, L2), dtype=torch.float32, device=q.device)  # softmax statistics
         status = _status(q.device)
         prob = _problem(q)
         with torch.cuda.device(q.device):
@@ -117,7 +117,7 @@ class _attention(torch.autograd.Function):
         dv = torch.empty_like(dq)
         db = torch.empty((B, H, L2, L2), dtype=b_pw.dtype, device=dev)
         db32 = torch.empty((B, H, L2, L2), dtype=torch.float32, device=dev)
-        delta = torch.empty_like(lse)
+        delta = torch.empty((B, H, L1, L2), dtype=torch.float32, device=dev)
         prob = _problem(q)
         L = _cabi.lib()
         ws_bytes = int(L.fta_bwd_workspace_bytes(prob))
