@@ -8,6 +8,7 @@
 namespace {
 
 thread_local int g_last_cuda_error = 0;
+thread_local cudaEvent_t g_prof_start = nullptr, g_prof_stop = nullptr;
 
 int cuda_fail(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);
@@ -215,7 +216,9 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
   for (int i = 0; i < 4; ++i) sb[i] = bias->stride[i];
   if (fta::launch_transpose_bias(bias->ptr, sb, bias_t, prob->B, prob->H, prob->L2, st) != 0)
     return cuda_fail(cudaGetLastError());
+  if (g_prof_start) cudaEventRecord(g_prof_start, st);
   if (fta::launch_bwd(a, st) != 0) return cuda_fail(cudaGetLastError());
+  if (g_prof_stop) cudaEventRecord(g_prof_stop, st);
   if (fta::launch_dq_finalize(dq32, dq->ptr, sdq, prob->B, prob->H, prob->L1, prob->L2, prob->D, sm_scale, bf16,
                               st) != 0)
     return cuda_fail(cudaGetLastError());
@@ -231,6 +234,12 @@ int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* 
   if (fta::launch_dbias_finalize(src, 1, n, nullptr, dst, dtype == FTA_BF16, static_cast<cudaStream_t>(stream)) !=
       0)
     return cuda_fail(cudaGetLastError());
+  return FTA_OK;
+}
+
+int fta_profile_backward_kernel(void* start_event, void* stop_event) {
+  g_prof_start = static_cast<cudaEvent_t>(start_event);
+  g_prof_stop = static_cast<cudaEvent_t>(stop_event);
   return FTA_OK;
 }
 

@@ -127,6 +127,13 @@ FTA_API int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaT
  * flash_tt_attn.py:425-426, 613). */
 FTA_API int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* stream);
 
+/* Profiling hook, off by default. After this call, every fta_backward on the calling thread
+ * records `start_event` right before and `stop_event` right after its main kernel (the
+ * tcgen05 backward kernel, excluding the memset, transpose and finalise kernels around it) on
+ * the stream it is given. Both are cudaEvent_t passed as void*; NULL, NULL switches it off.
+ * No counterpart in the reference (it times whole calls with do_bench, flash_tt_attn.py:804). */
+FTA_API int fta_profile_backward_kernel(void* start_event, void* stop_event);
+
 /* Copies the status word to the host and synchronises `stream`. Returns FTA_OK when it is
  * zero, FTA_ERR_DEVICE otherwise; `*code_out` (host pointer, may be NULL) receives the raw
  * word: 0x1000 | site for a wait that ran out. */
