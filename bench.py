@@ -149,6 +149,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="restrict the workload to its first ROWS L1 rows (a small case for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -173,6 +176,8 @@ def main():
     warmup = max(3, args.warmup)
 
     w = workloads.WORKLOADS[WORKLOAD]
+    if args.rows > 0:
+        w = w.with_rows(min(args.rows, w.L1))
     rows = fta.shard_rows(w.L1, rank, world)
     nrows = rows.stop - rows.start
     dt = torch.bfloat16
@@ -289,7 +294,10 @@ def main():
         out_host["dv"].copy_(t_["v"].grad, non_blocking=True)
         db_host.copy_(t_["bias"].grad, non_blocking=True)
 
-    e2e_step()
+    if args.no_e2e:
+        e2e_steps = 0
+    else:
+        e2e_step()
     barrier()
     e2e_ms = []
     for _ in range(e2e_steps):
@@ -303,7 +311,7 @@ def main():
     te = torch.tensor([float(np.sum(e2e_ms))], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_value = flops_step * e2e_steps / (float(te.item()) * 1e-3) / 1e12
+    e2e_value = flops_step * e2e_steps / (float(te.item()) * 1e-3) / 1e12 if e2e_steps else None
     fta.check_device_status(dev)
 
     if rank == 0:
@@ -315,7 +323,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "B": B, "H": H, "L1": w.L1, "L2": L2, "D": D,
+            "config": {"workload": WORKLOAD if args.rows <= 0 else f"{WORKLOAD}[first {w.L1} rows]", "B": B, "H": H, "L1": w.L1, "L2": L2, "D": D,
                        "rows_per_gpu": nrows, "parallelism": f"L1 rows sharded over {world} GPU(s)",
                        "l2": "flushed between steps (256 MB write outside the events)",
                        "fwd_ms": float(np.mean(fwd_ms)), "bwd_kernel_ms": bwd_kernel_ms,
