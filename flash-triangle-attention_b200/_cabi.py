@@ -39,7 +39,7 @@ _lib = None
 EXPORTS = (
     "fta_version", "fta_strerror", "fta_last_cuda_error", "fta_forward", "fta_bwd_preprocess",
     "fta_bwd_workspace_bytes", "fta_bwd_num_planes", "fta_backward", "fta_dbias_cast",
-    "fta_read_status", "fta_profile_backward_kernel",
+    "fta_read_status", "fta_profile_backward_kernel", "fta_backward_noalloc", "fta_noalloc_max_bytes",
 )
 
 
@@ -73,6 +73,10 @@ def lib():
     L.fta_dbias_cast.argtypes = [vp, vp, ctypes.c_int64, ctypes.c_int32, vp]
     L.fta_read_status.restype = ctypes.c_int
     L.fta_read_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
+    L.fta_backward_noalloc.restype = ctypes.c_int
+    L.fta_backward_noalloc.argtypes = [PP, P5, P5, P5, P4, P5, vp, vp, f32, P5, P5, P5, vp, vp, vp, vp]
+    L.fta_noalloc_max_bytes.restype = ctypes.c_size_t
+    L.fta_noalloc_max_bytes.argtypes = []
     L.fta_profile_backward_kernel.restype = ctypes.c_int
     L.fta_profile_backward_kernel.argtypes = [vp, vp]
     _lib = L

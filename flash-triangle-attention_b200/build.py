@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfta.so")
-SOURCES = ["api.cu", "fwd_sm100.cu", "bwd_sm100.cu", "stream_kernels.cu"]
+SOURCES = ["api.cu", "fwd_sm100.cu", "bwd_sm100.cu", "stream_kernels.cu", "noalloc.cu"]
 HEADERS = ["tc05.cuh", "tmap.h", "fta_kernels.h", os.path.join("..", "..", "include", "fta.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",

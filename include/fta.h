@@ -127,6 +127,28 @@ FTA_API int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaT
  * flash_tt_attn.py:425-426, 613). */
 FTA_API int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* stream);
 
+/* Backward pass without a caller-provided workspace. It has no counterpart in the reference.
+ * For callers that cannot allocate device memory where they call this library (a framework's
+ * memory-planning phase, a plugin interface that only passes inputs and outputs, a loop that
+ * forbids cudaMalloc): same arguments and results as fta_backward, but the scratch memory is a
+ * fixed array inside the library, fta_noalloc_max_bytes() long (64 MiB), present once on every
+ * GPU that loads the library until the process exits. Nothing is allocated or freed.
+ *  - Problems whose fta_bwd_workspace_bytes() exceeds that size are rejected with
+ *    FTA_ERR_TOO_LARGE before anything is launched.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current); make that first call before any stream capture.
+ *  - All calls on a device share the one array: two calls whose work overlaps on the GPU
+ *    (different streams, different threads) race on it. Keep them on one stream, or order them.
+ *    The array keeps what the last call wrote; each call clears or overwrites what it reads. */
+FTA_API int fta_backward_noalloc(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
+                                 const FtaTensor5* v, const FtaTensor4* bias, const FtaTensor5* dout,
+                                 const float* lse, const float* delta, float sm_scale,
+                                 const FtaTensor5* dq, const FtaTensor5* dk, const FtaTensor5* dv,
+                                 float* dbias_f32, void* dbias_cast, int32_t* status, void* stream);
+
+/* Size in bytes of the fixed scratch array used by fta_backward_noalloc. */
+FTA_API size_t fta_noalloc_max_bytes(void);
+
 /* Profiling hook, off by default. After this call, every fta_backward on the calling thread
  * records `start_event` right before and `stop_event` right after its main kernel (the
  * tcgen05 backward kernel, excluding the memset, transpose and finalise kernels around it) on

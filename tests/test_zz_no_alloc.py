@@ -1,0 +1,91 @@
+"""fta_backward_noalloc: the backward pass for callers that cannot allocate device memory
+(framework memory-planning phases, plugin interfaces that pass only inputs and outputs, loops
+that forbid cudaMalloc). Its scratch is a fixed 64 MiB array inside the library; the results
+must equal those of fta_backward, which takes a caller-allocated workspace.
+
+Collected last on purpose: a run that stops at the first failure has then run every other test.
+"""
+import numpy as np
+import pytest
+import torch
+
+import _cabi
+import workloads
+from _cabi import FtaProblem, t4, t5
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup():
+    w = workloads.Workload("noalloc", 1, 2, 7, 256, 32, "bf16", seed=41)
+    x = workloads.make_inputs(w)
+    d = {k: torch.from_numpy(x[k]).cuda().to(torch.bfloat16) for k in ("q", "k", "v", "do", "bias")}
+    B, H, L1, L2, D = w.B, w.H, w.L1, w.L2, w.D
+    prob = FtaProblem(B, H, L1, L2, D, _cabi.FTA_BF16)
+    L = _cabi.lib()
+    o = torch.empty_like(d["q"])
+    lse = torch.empty(2, B, H, L1, L2, dtype=torch.float32, device="cuda")
+    delta = torch.empty(B, H, L1, L2, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _cabi.check(L.fta_forward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), w.sm_scale, t5(o),
+                              lse.data_ptr(), status.data_ptr(), st), "fta_forward")
+    _cabi.check(L.fta_bwd_preprocess(prob, t5(o), t5(d["do"]), delta.data_ptr(), st), "fta_bwd_preprocess")
+    return w, d, prob, L, lse, delta, status, st
+
+
+def _outputs(d):
+    return {"dq": torch.empty_like(d["q"]), "dk": torch.empty_like(d["q"]), "dv": torch.empty_like(d["q"]),
+            "db": torch.empty_like(d["bias"]),
+            "db32": torch.empty(d["bias"].shape, dtype=torch.float32, device="cuda")}
+
+
+def test_noalloc_backward_matches_workspace_backward_twice():
+    w, d, prob, L, lse, delta, status, st = _setup()
+    need = int(L.fta_bwd_workspace_bytes(prob))
+    assert 0 < need <= int(L.fta_noalloc_max_bytes())
+    ref = _outputs(d)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    _cabi.check(L.fta_backward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), t5(d["do"]),
+                               lse.data_ptr(), delta.data_ptr(), w.sm_scale, t5(ref["dq"]), t5(ref["dk"]),
+                               t5(ref["dv"]), ref["db32"].data_ptr(), ref["db"].data_ptr(), ws.data_ptr(), need,
+                               status.data_ptr(), st), "fta_backward")
+    torch.cuda.synchronize()
+    for call in range(2):  # the second call finds the first call's leftovers in the fixed array
+        got = _outputs(d)
+        for t in got.values():
+            t.fill_(float("nan"))
+        _cabi.check(L.fta_backward_noalloc(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), t5(d["do"]),
+                                           lse.data_ptr(), delta.data_ptr(), w.sm_scale, t5(got["dq"]),
+                                           t5(got["dk"]), t5(got["dv"]), got["db32"].data_ptr(),
+                                           got["db"].data_ptr(), status.data_ptr(), st), "fta_backward_noalloc")
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        for k in ref:
+            a, b = got[k].float().cpu().numpy(), ref[k].float().cpu().numpy()
+            assert not np.isnan(a).any(), (k, call)
+            # same kernels on the same inputs: dK, dV, dBias are fixed-order sums (equal); dQ is a
+            # float32 reduction over key blocks whose order may differ -> the suite's tolerance
+            assert np.max(np.abs(a - b)) <= 2e-2, (k, call, float(np.max(np.abs(a - b))))
+            if k in ("dk", "dv", "db32", "db"):
+                assert np.array_equal(a, b), (k, call)
+
+
+def test_noalloc_rejects_problems_beyond_the_fixed_array():
+    L = _cabi.lib()
+    big = FtaProblem(1, 4, 768, 768, 32, _cabi.FTA_BF16)   # needs hundreds of MB of scratch
+    assert int(L.fta_bwd_workspace_bytes(big)) > int(L.fta_noalloc_max_bytes())
+    x = torch.zeros(8, dtype=torch.bfloat16, device="cuda")
+    f = torch.zeros(8, dtype=torch.float32, device="cuda")
+    s = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fake5 = _cabi.FtaTensor5()
+    fake5.ptr = x.data_ptr()
+    for i, v in enumerate((1 << 30, 1 << 28, 768 * 32, 32, 1)):
+        fake5.stride[i] = v
+    fake4 = _cabi.FtaTensor4()
+    fake4.ptr = x.data_ptr()
+    for i, v in enumerate((1 << 24, 768 * 768, 768, 1)):
+        fake4.stride[i] = v
+    rc = L.fta_backward_noalloc(big, fake5, fake5, fake5, fake4, fake5, f.data_ptr(), f.data_ptr(), 1.0, fake5,
+                                fake5, fake5, f.data_ptr(), None, s.data_ptr(), None)
+    assert rc == -11 and "maximum" in _cabi.strerror(rc)
