@@ -24,9 +24,10 @@
 // run to run; the planes are summed in fixed order by the finalise kernel.
 // dQ leaves the CTA as float32 reductions into a zero-initialised buffer (sum over key blocks).
 //
-//   warps 0-3 : compute warpgroup 0 (queries 0..63 of the tile)   also stores dV
-//   warps 4-7 : compute warpgroup 1 (queries 64..127)             also reduces dQ, stores dK
-//   warp 8    : TMA producer      warp 9 : tcgen05 issuer      warps 10-11 : idle
+//   warp 0     : tcgen05 issuer (lowest warp id: the scheduler prefers older warps)
+//   warp 1     : TMA producer        warps 2-3 : idle
+//   warps 4-7  : compute warpgroup 0 (queries 0..63 of the tile)   also stores dV
+//   warps 8-11 : compute warpgroup 1 (queries 64..127)             also reduces dQ, stores dK
 // Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
 #include "fta_kernels.h"
 #include "tc05.cuh"
@@ -44,8 +45,14 @@ __device__ unsigned long long g_trace_bwd[8192];
     if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile) < 64)                 \
       g_trace_bwd[((role) * 64 + (tile)) * 8 + (ev)] = clock64();                  \
   } while (0)
+// same, but kept in shared memory until the end of the kernel (no global store on the way)
+#define FTA_SSTAMP(ev, tile)                                                       \
+  do {                                                                             \
+    if (blockIdx.x == 0 && (tile) < 32) s_trace[(tile) * 8 + (ev)] = clock64();    \
+  } while (0)
 #else
 #define FTA_STAMP(role, ev, tile) do { } while (0)
+#define FTA_SSTAMP(ev, tile) do { } while (0)
 #endif
 
 template <int kD>
@@ -73,7 +80,7 @@ struct BwdCfg {
   static constexpr int B_ACCFULL = B_DQDONE + 1;
   static constexpr int B_ACCFREE = B_ACCFULL + 1;
   static constexpr int NBAR = B_ACCFREE + 1;
-  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024 + 2048 + 16;  // + trace slots (debug builds)
   static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
   static constexpr uint32_t ROW_B = kD * 2;
   static constexpr uint32_t SBO = 8 * ROW_B;
@@ -131,6 +138,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+#ifdef FTA_TRACE
+  unsigned long long* s_trace = reinterpret_cast<unsigned long long*>(abort_flag + 3);
+#endif
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
@@ -144,6 +154,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int ngroups = (ngroups_total - r + p.NP - 1) / p.NP;  // groups r, r+NP, ...
   const WaitCtx w{abort_flag, p.status};
 
+#ifdef FTA_TRACE
+  if (threadIdx.x < 256) s_trace[threadIdx.x] = 0;
+#endif
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar(C::B_KVFULL), 1);
@@ -163,7 +176,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(bar(C::B_ACCFREE), 8);
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -172,9 +185,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tbase = *tmem_slot;
 
-  if (warp >= 8) {
+  if (warp < 4) {
     reg_dec<88>();
-    if (warp == 8) {
+    if (warp == 1) {
       // ---------------------------------------------------------------- TMA producer
       if (elect_one()) {
         tma_prefetch_desc(&tmQ);
@@ -228,7 +241,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
       }
-    } else if (warp == 9) {
+    } else if (warp == 0) {
       // ---------------------------------------------------------------- MMA issuer
       constexpr int fmt = kBf16 ? 1 : 0;
       constexpr uint32_t idesc_s = umma_idesc_f16(fmt, 128, 64, 0, 0);    // S^T, dP^T halves
@@ -248,6 +261,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint64_t dQ = umma_smem_desc(st + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
         const uint64_t dO = umma_smem_desc(st + C::TILE_B + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
         if (elect_one()) {
+
 #pragma unroll
           for (int ks = 0; ks < kD / 16; ++ks)
             umma_ss(tbase + C::TM_ST + wh * 64, dK + ks * 2, dQ + ks * 2, idesc_s, ks > 0);
@@ -270,10 +284,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int jb = t / Gc, g = t % Gc, s = tt % C::NQ;
           const uint32_t st = sQDO_a + s * C::STAGE_B;
           for (int wh = 0; wh < 2 && ok; ++wh) {
-            FTA_STAMP(2, wh * 3 + 0, tt);
+            // (issuer-side global stamps removed: they perturb the issue timing)
             ok = mbar_wait_warp(bar(C::B_PFULL + wh), tt & 1, w, 0x33);
             if (!ok) break;
-            FTA_STAMP(2, wh * 3 + 1, tt);
+            // (issuer-side global stamps removed: they perturb the issue timing)
             if (t == 0 && wh == 0 && n > 0) {
               ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
               if (!ok) break;
@@ -283,6 +297,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const uint64_t dQm = umma_smem_desc(st + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
             const uint32_t tdk = tbase + C::TM_ACC + g * 2 * kD, tdv = tdk + kD;
             const uint32_t acc_first = (jb > 0 || wh > 0) ? 1u : 0u;
+            
             if (elect_one()) {
 #pragma unroll
               for (int ks = 0; ks < 4; ++ks)
@@ -292,6 +307,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               for (int ks = 0; ks < 4; ++ks)
                 umma_ts(tdk, tbase + C::TM_DP + wh * 64 + ks * 8, dQm + ks * ((2 * C::SBO) >> 4), idesc_acc,
                         ks > 0 ? 1u : acc_first);
+              
               if (wh == 1) {
                 const uint64_t dSm = umma_smem_desc(sDS_a, 16384, 1024, kSwz128);
                 const uint64_t dKm = umma_smem_desc(sKV_a + g * 2 * C::TILE_B, C::SBO, C::SBO, C::SWZ);
@@ -305,7 +321,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             __syncwarp();
             if (t + 1 < T) ok = issue_sdp(tt + 1, (t + 1) % Gc, wh, wh == 0);
-            FTA_STAMP(2, wh * 3 + 2, tt);
+            // (issuer-side global stamps removed: they perturb the issue timing)
           }
         }
         if (ok) {
@@ -320,7 +336,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------------ compute warpgroups
     reg_inc<208>();
-    const int wh = warp >> 2;                 // which 64-query half of the tile
+    const int wh = (warp >> 2) - 1;           // which 64-query half of the tile
     const int key = (warp & 3) * 32 + lane;   // key row of the block == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tST = tbase + C::TM_ST + wh * 64 + lane_off;
@@ -355,6 +371,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int bs = nb & 1;
         ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
         if (!ok) break;
+        if ((warp & 3) == 0) FTA_STAMP(wh, 7, tt);
         const uint8_t* brow = sBias + bs * C::BIAS_B + wh * 16384 + key * 128;
         for (int g = 0; g < Gc; ++g, ++tt) {
           const int s = tt % C::NQ;
@@ -366,6 +383,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!ok) break;
           if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
           tc_fence_after_sync();
+          if ((warp & 3) == 0 && wh == 0) FTA_SSTAMP(4, tt + 16);
           const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + wh * 16;
           const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + wh * 16;
           const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1024) + wh * 16;
@@ -376,6 +394,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tmem_ld32(tST + cc * 32, sv);
             tmem_ld32(tDP + cc * 32, dv);
             tmem_ld_wait();
+            if ((warp & 3) == 0 && wh == 0) FTA_SSTAMP(cc * 2, tt + 16);
             uint32_t pp[16];
 #pragma unroll
             for (int c8 = 0; c8 < 4; ++c8) {
@@ -408,6 +427,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             tmem_st16(tST + cc * 16, pp);
             tmem_st16(tDP + cc * 16, dd + cc * 16);
+            if ((warp & 3) == 0 && wh == 0) FTA_SSTAMP(cc * 2 + 1, tt + 16);
           }
           if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
@@ -435,6 +455,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if ((warp & 3) == 0) FTA_STAMP(wh, 4, tt);
         }
         if (!ok) break;
+        if ((warp & 3) == 0) FTA_STAMP(wh, 5, tt - 1);
         // bias stage no longer needed by this warp
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
@@ -457,6 +478,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             red_add(dst + static_cast<long long>(2 * c + 1) * p.L2, a1);
           }
         }
+        if ((warp & 3) == 0) FTA_STAMP(wh, 6, tt - 1);
       }
       if (!ok) break;
       // ---- group epilogue: last dQ tile, then dK / dV of the G rows
@@ -503,7 +525,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) __nanosleep(20000);
-  if (warp == 9) tmem_dealloc(tbase, 512);
+  if (warp == 0) tmem_dealloc(tbase, 512);
+#ifdef FTA_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (int i = 0; i < 256; ++i) g_trace_bwd[3 * 512 + i] = s_trace[i];
+#endif
 }
 
 template <int kD, bool kBf16>

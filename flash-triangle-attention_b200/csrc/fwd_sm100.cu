@@ -5,12 +5,14 @@
 // (b,h). It walks the key blocks once (outer loop) and, inside, the G rows (inner loop), so
 // that one 128x128 bias tile staged in shared memory serves G score tiles:
 //
-//   warp 8      : TMA producer  (Q tiles once, K/V ring, bias double buffer)
-//   warp 9      : tcgen05 issuer (S = Q K^T into TMEM, O += P V with P read from TMEM)
-//   warps 0-3   : softmax warpgroup 0 -> even rows of the group, S/P buffer 0
-//   warps 4-7   : softmax warpgroup 1 -> odd rows of the group,  S/P buffer 1
-//   warps 10-11 : idle; warps 8-11 form a warpgroup that hands most of its registers to the
-//                 softmax warpgroups (setmaxnreg)
+//   warp 0      : tcgen05 issuer (S = Q K^T into TMEM, O += P V with P read from TMEM)
+//   warp 1      : TMA producer  (Q tiles once, K/V ring, bias double buffer)
+//   warps 2-3   : idle; warps 0-3 form a warpgroup that hands most of its registers to the
+//                 softmax warpgroups (setmaxnreg). The issuer has the lowest warp id so that
+//                 the warp scheduler, which prefers older warps, never starves it behind the
+//                 long instruction runs of the softmax warps.
+//   warps 4-7   : softmax warpgroup 0 -> even rows of the group, S/P buffer 0
+//   warps 8-11  : softmax warpgroup 1 -> odd rows of the group,  S/P buffer 1
 //
 // The producer and issuer loops run warp-uniformly (all 32 lanes) and only the TMA / MMA
 // instruction itself is issued by one elected lane, so that descriptors and addresses stay
@@ -143,7 +145,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     mbar_fence_init();
   }
-  if (warp == 9) {
+  if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), 512);
     tmem_relinquish();
   }
@@ -152,9 +154,9 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_after_sync();
   const uint32_t tbase = *tmem_slot;
 
-  if (warp >= 8) {
+  if (warp < 4) {
     reg_dec<88>();
-    if (warp == 8) {
+    if (warp == 1) {
       // ---------------------------------------------------------------- TMA producer
       if (elect_one()) {
         tma_prefetch_desc(&tmQ);
@@ -193,7 +195,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         }
       }
-    } else if (warp == 9) {
+    } else if (warp == 0) {
       // ---------------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc_qk = umma_idesc_f16(kBf16 ? 1 : 0, 128, 128, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(kBf16 ? 1 : 0, 128, kD, 0, 1);
@@ -248,7 +250,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
     reg_inc<208>();
-    const int wg = warp >> 2;
+    const int wg = (warp >> 2) - 1;
     const int row = (warp & 3) * 32 + lane;  // query row of the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tbase + wg * 128 + lane_off;
@@ -415,7 +417,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) __nanosleep(20000);  // let copies already in flight land before the CTA exits
-  if (warp == 9) tmem_dealloc(tbase, 512);
+  if (warp == 0) tmem_dealloc(tbase, 512);
 }
 
 template <int kD, bool kBf16>

@@ -326,7 +326,26 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-// Two fp32 lanes in one 64-bit register: Blackwell issues fma / add / mul on both at once.
+// Two fp32 lanes handled together. Packed build: one 64-bit register, Blackwell issues fma /
+// add / mul on both lanes at once. FTA_SCALAR_MATH build: two plain registers (for comparison).
+#ifdef FTA_SCALAR_MATH
+struct f32x2 { float lo, hi; };
+__device__ __forceinline__ f32x2 mk2(float lo, float hi) { return f32x2{lo, hi}; }
+__device__ __forceinline__ void un2(f32x2 v, float& lo, float& hi) { lo = v.lo; hi = v.hi; }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  return f32x2{fmaf(a.lo, b.lo, c.lo), fmaf(a.hi, b.hi, c.hi)};
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { return f32x2{a.lo + b.lo, a.hi + b.hi}; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return f32x2{a.lo * b.lo, a.hi * b.hi}; }
+#elif !defined(FTA_ASM_F32X2)
+// the compiler's own f32x2 intrinsics: it does the register pairing itself
+typedef float2 f32x2;
+__device__ __forceinline__ f32x2 mk2(float lo, float hi) { return make_float2(lo, hi); }
+__device__ __forceinline__ void un2(f32x2 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return __fmul2_rn(a, b); }
+#else
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 mk2(float lo, float hi) {
   f32x2 r;
@@ -351,6 +370,7 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+#endif
 
 // pack two fp32 into bf16x2 / f16x2 (lo in the low half), round to nearest even
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -1,0 +1,54 @@
+"""Row-sharded run on 2 GPUs (NCCL): each rank owns half of the L1 rows, the bias is replicated,
+the backward all-reduces the float32 dBias. Runs as child processes; skipped with < 2 GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+_WORKER = r"""
+import os, sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "flash-triangle-attention_b200"))
+import numpy as np, torch, torch.distributed as dist
+import flash_tt_attn as fta, workloads
+from oracle import tt_attn_oracle as npo
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+w = workloads.Workload("t", 1, 2, 10, 256, 32, "bf16", 13)
+rows = fta.shard_rows(w.L1, rank, world)
+x = workloads.make_inputs(w, rows)
+t = {{k: torch.from_numpy(x[k]).cuda().to(torch.bfloat16) for k in ("q", "k", "v", "do", "bias")}}
+for k in ("q", "k", "v", "bias"):
+    t[k].requires_grad_()
+o = fta.attention(t["q"], t["k"], t["v"], t["bias"], w.sm_scale, group=dist.group.WORLD)
+o.backward(t["do"])
+torch.cuda.synchronize(); fta.check_device_status()
+full = workloads.make_inputs(w)
+r = {{k: torch.from_numpy(full[k]).to(torch.bfloat16).float().numpy() for k in ("q", "k", "v", "do", "bias")}}
+ref = npo.forward_backward(r["q"], r["k"], r["v"], r["bias"], r["do"], w.sm_scale)
+got = {{"o": o, "dq": t["q"].grad, "dk": t["k"].grad, "dv": t["v"].grad}}
+for k, v in got.items():
+    g = v.detach().float().cpu().numpy()
+    assert npo.max_abs(g, ref[k][:, :, rows]) <= 2e-2 and npo.rel_l2(g, ref[k][:, :, rows]) <= 1e-2, k
+db = fta.last_dbias_f32().cpu().numpy()          # all-reduced: the full dBias on every rank
+assert npo.max_abs(db, ref["dbias"]) <= 2e-2 and npo.rel_l2(db, ref["dbias"]) <= 1e-2
+assert npo.rel_l2(t["bias"].grad.float().cpu().numpy(), ref["dbias"]) <= 1e-2
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_row_sharding_matches_oracle(tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER.format(root=ROOT))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 400), str(script)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
