@@ -25,7 +25,7 @@
 // dQ leaves the CTA as float32 reductions into a zero-initialised buffer (sum over key blocks).
 //
 //   warp 0     : tcgen05 issuer (lowest warp id: the scheduler prefers older warps)
-//   warp 1     : TMA producer        warps 2-3 : idle
+//   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : idle
 //   warps 4-7  : compute warpgroup 0 (queries 0..63 of the tile)   also stores dV
 //   warps 8-11 : compute warpgroup 1 (queries 64..127)             also reduces dQ, stores dK
 // Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
@@ -75,8 +75,10 @@ struct BwdCfg {
   static constexpr int B_BIASFULL = B_QDOEMPTY + NQ;
   static constexpr int B_BIASEMPTY = B_BIASFULL + 2;
   static constexpr int B_SFULL = B_BIASEMPTY + 2;
-  static constexpr int B_PFULL = B_SFULL + 2;
-  static constexpr int B_DQDONE = B_PFULL + 2;
+  static constexpr int B_DPFULL = B_SFULL + 2;
+  static constexpr int B_P1FULL = B_DPFULL + 2;
+  static constexpr int B_P2FULL = B_P1FULL + 2;
+  static constexpr int B_DQDONE = B_P2FULL + 2;
   static constexpr int B_ACCFULL = B_DQDONE + 1;
   static constexpr int B_ACCFREE = B_ACCFULL + 1;
   static constexpr int NBAR = B_ACCFREE + 1;
@@ -160,7 +162,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar(C::B_KVFULL), 1);
-    mbar_init(bar(C::B_KVFREE), 1);
+    mbar_init(bar(C::B_KVFREE), 2);  // main issuer + dQ issuer
     for (int i = 0; i < C::NQ; ++i) {
       mbar_init(bar(C::B_QDOFULL + i), 1);
       mbar_init(bar(C::B_QDOEMPTY + i), 1);
@@ -169,7 +171,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(bar(C::B_BIASFULL + i), 1);
       mbar_init(bar(C::B_BIASEMPTY + i), 8);
       mbar_init(bar(C::B_SFULL + i), 1);
-      mbar_init(bar(C::B_PFULL + i), 4);  // one arrive per warp of the warpgroup
+      mbar_init(bar(C::B_DPFULL + i), 1);
+      mbar_init(bar(C::B_P1FULL + i), 4);  // one arrive per warp of the warpgroup
+      mbar_init(bar(C::B_P2FULL + i), 4);
     }
     mbar_init(bar(C::B_DQDONE), 1);
     mbar_init(bar(C::B_ACCFULL), 1);
@@ -243,85 +247,77 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
     } else if (warp == 0) {
       // ---------------------------------------------------------------- MMA issuer
+      // Two hand-overs per tile and half: after phase 1 (P^T written) it issues dV and the next
+      // tile's S^T of that half; after phase 2 (dS^T written) dK and the next tile's dP^T. The
+      // next S^T / dP^T are therefore in flight while the compute warps are still busy.
       constexpr int fmt = kBf16 ? 1 : 0;
       constexpr uint32_t idesc_s = umma_idesc_f16(fmt, 128, 64, 0, 0);    // S^T, dP^T halves
       constexpr uint32_t idesc_acc = umma_idesc_f16(fmt, 128, kD, 0, 1);  // dV, dK (A in TMEM, B M-major)
-      constexpr uint32_t idesc_dq = umma_idesc_f16(fmt, 128, kD, 1, 1);   // dQ (A, B M-major)
-      const uint32_t sKV_a = smem_u32(sKV), sQDO_a = smem_u32(sQDO), sDS_a = smem_u32(sDS);
+      const uint32_t sKV_a = smem_u32(sKV), sQDO_a = smem_u32(sQDO);
       bool ok = true;
       int tt = 0;
-      // S^T_w / dP^T_w of the tile with ring index `tix`, row g of the group
-      auto issue_sdp = [&](int tix, int g, int wh, bool wait_stage) -> bool {
-        const int s = tix % C::NQ;
-        if (wait_stage && !mbar_wait_warp(bar(C::B_QDOFULL + s), (tix / C::NQ) & 1, w, 0x31)) return false;
-        tc_fence_after_sync();
-        const uint32_t st = sQDO_a + s * C::STAGE_B;
-        const uint64_t dK = umma_smem_desc(sKV_a + g * 2 * C::TILE_B, 16, C::SBO, C::SWZ);
-        const uint64_t dV = umma_smem_desc(sKV_a + g * 2 * C::TILE_B + C::TILE_B, 16, C::SBO, C::SWZ);
-        const uint64_t dQ = umma_smem_desc(st + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
-        const uint64_t dO = umma_smem_desc(st + C::TILE_B + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
+      // S^T_w (which == 0) or dP^T_w (which == 1) of the tile with ring index `tix`, row g
+      auto issue_half = [&](int which, int tix, int g, int wh) {
+        const uint32_t st = sQDO_a + (tix % C::NQ) * C::STAGE_B;
+        const uint64_t dA = umma_smem_desc(sKV_a + g * 2 * C::TILE_B + which * C::TILE_B, 16, C::SBO, C::SWZ);
+        const uint64_t dB = umma_smem_desc(st + which * C::TILE_B + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
+        const uint32_t td = tbase + (which ? C::TM_DP : C::TM_ST) + wh * 64;
         if (elect_one()) {
-
 #pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks)
-            umma_ss(tbase + C::TM_ST + wh * 64, dK + ks * 2, dQ + ks * 2, idesc_s, ks > 0);
-#pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks)
-            umma_ss(tbase + C::TM_DP + wh * 64, dV + ks * 2, dO + ks * 2, idesc_s, ks > 0);
-          umma_commit(bar(C::B_SFULL + wh));
+          for (int ks = 0; ks < kD / 16; ++ks) umma_ss(td, dA + ks * 2, dB + ks * 2, idesc_s, ks > 0);
+          umma_commit(bar((which ? C::B_DPFULL : C::B_SFULL) + wh));
         }
         __syncwarp();
-        return true;
+      };
+      // dV_g += P^T_w dO_w (which == 0) or dK_g += dS^T_w Q_w (which == 1)
+      auto issue_acc = [&](int which, int tix, int g, int wh, uint32_t acc_first) {
+        const uint32_t st = sQDO_a + (tix % C::NQ) * C::STAGE_B;
+        const uint64_t dB =
+            umma_smem_desc(st + (which ? 0 : C::TILE_B) + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
+        const uint32_t td = tbase + C::TM_ACC + g * 2 * kD + (which ? 0 : kD);
+        const uint32_t ta = tbase + (which ? C::TM_DP : C::TM_ST) + wh * 64;
+        if (elect_one()) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_ts(td, ta + ks * 8, dB + ks * ((2 * C::SBO) >> 4), idesc_acc, ks > 0 ? 1u : acc_first);
+        }
+        __syncwarp();
       };
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = (r + n * p.NP) * G;
         const int Gc = min(G, p.L1 - i0);
         const int T = nq * Gc;
-        ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32);
+        ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32) &&
+             mbar_wait_warp(bar(C::B_QDOFULL + tt % C::NQ), (tt / C::NQ) & 1, w, 0x31);
         if (!ok) break;
-        ok = issue_sdp(tt, 0, 0, true) && issue_sdp(tt, 0, 1, false);
+        tc_fence_after_sync();
+        issue_half(0, tt, 0, 0);
+        issue_half(0, tt, 0, 1);
+        issue_half(1, tt, 0, 0);
+        issue_half(1, tt, 0, 1);
         for (int t = 0; t < T && ok; ++t, ++tt) {
-          const int jb = t / Gc, g = t % Gc, s = tt % C::NQ;
-          const uint32_t st = sQDO_a + s * C::STAGE_B;
-          for (int wh = 0; wh < 2 && ok; ++wh) {
-            // (issuer-side global stamps removed: they perturb the issue timing)
-            ok = mbar_wait_warp(bar(C::B_PFULL + wh), tt & 1, w, 0x33);
+          const int jb = t / Gc, g = t % Gc, gn = (t + 1) % Gc;
+          const bool more = t + 1 < T;
+          for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 1 done: dV, then the next S^T
+            ok = mbar_wait_warp(bar(C::B_P1FULL + wh), tt & 1, w, 0x33);
+            if (ok && t == 0 && wh == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
+            if (ok && more && wh == 0)
+              ok = mbar_wait_warp(bar(C::B_QDOFULL + (tt + 1) % C::NQ), ((tt + 1) / C::NQ) & 1, w, 0x35);
             if (!ok) break;
-            // (issuer-side global stamps removed: they perturb the issue timing)
-            if (t == 0 && wh == 0 && n > 0) {
-              ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
-              if (!ok) break;
-            }
             tc_fence_after_sync();
-            const uint64_t dOm = umma_smem_desc(st + C::TILE_B + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
-            const uint64_t dQm = umma_smem_desc(st + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
-            const uint32_t tdk = tbase + C::TM_ACC + g * 2 * kD, tdv = tdk + kD;
-            const uint32_t acc_first = (jb > 0 || wh > 0) ? 1u : 0u;
-            
-            if (elect_one()) {
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                umma_ts(tdv, tbase + C::TM_ST + wh * 64 + ks * 8, dOm + ks * ((2 * C::SBO) >> 4), idesc_acc,
-                        ks > 0 ? 1u : acc_first);
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                umma_ts(tdk, tbase + C::TM_DP + wh * 64 + ks * 8, dQm + ks * ((2 * C::SBO) >> 4), idesc_acc,
-                        ks > 0 ? 1u : acc_first);
-              
-              if (wh == 1) {
-                const uint64_t dSm = umma_smem_desc(sDS_a, 16384, 1024, kSwz128);
-                const uint64_t dKm = umma_smem_desc(sKV_a + g * 2 * C::TILE_B, C::SBO, C::SBO, C::SWZ);
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks)
-                  umma_ss(tbase + C::TM_DQ + (tt & 1) * kD, dSm + ks * (2048 >> 4),
-                          dKm + ks * ((2 * C::SBO) >> 4), idesc_dq, ks > 0);
-                umma_commit(bar(C::B_QDOEMPTY + s));
-                umma_commit(bar(C::B_DQDONE));
-              }
+            issue_acc(0, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
+            if (more) issue_half(0, tt + 1, gn, wh);
+          }
+          for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 2 done: dK, then the next dP^T
+            ok = mbar_wait_warp(bar(C::B_P2FULL + wh), tt & 1, w, 0x39);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_acc(1, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
+            if (wh == 1) {  // every MMA that reads this Q/dO stage has been issued
+              if (elect_one()) umma_commit(bar(C::B_QDOEMPTY + tt % C::NQ));
+              __syncwarp();
             }
-            __syncwarp();
-            if (t + 1 < T) ok = issue_sdp(tt + 1, (t + 1) % Gc, wh, wh == 0);
-            // (issuer-side global stamps removed: they perturb the issue timing)
+            if (more) issue_half(1, tt + 1, gn, wh);
           }
         }
         if (ok) {
@@ -329,6 +325,41 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             umma_commit(bar(C::B_ACCFULL));
             umma_commit(bar(C::B_KVFREE));
           }
+          __syncwarp();
+        }
+      }
+    } else if (warp == 2) {
+      // ---------------------------------------------------------------- dQ issuer
+      // dQ = dS K needs the dS rows of both halves; it writes its own TMEM columns and reads no
+      // Q/dO stage, so it is issued from a second warp and does not hold up the main issuer.
+      constexpr uint32_t idesc_dq = umma_idesc_f16(kBf16 ? 1 : 0, 128, kD, 1, 1);  // A, B M-major
+      const uint32_t sKV_a = smem_u32(sKV), sDS_a = smem_u32(sDS);
+      bool ok = true;
+      int tt = 0;
+      for (int n = 0; n < ngroups && ok; ++n) {
+        const int i0 = (r + n * p.NP) * G;
+        const int Gc = min(G, p.L1 - i0);
+        const int T = nq * Gc;
+        ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x36);
+        for (int t = 0; t < T && ok; ++t, ++tt) {
+          const int g = t % Gc;
+          ok = mbar_wait_warp(bar(C::B_P2FULL + 0), tt & 1, w, 0x37) &&
+               mbar_wait_warp(bar(C::B_P2FULL + 1), tt & 1, w, 0x38);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t dSm = umma_smem_desc(sDS_a, 16384, 1024, kSwz128);
+          const uint64_t dKm = umma_smem_desc(sKV_a + g * 2 * C::TILE_B, C::SBO, C::SBO, C::SWZ);
+          if (elect_one()) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              umma_ss(tbase + C::TM_DQ + (tt & 1) * kD, dSm + ks * (2048 >> 4), dKm + ks * ((2 * C::SBO) >> 4),
+                      idesc_dq, ks > 0);
+            umma_commit(bar(C::B_DQDONE));
+          }
+          __syncwarp();
+        }
+        if (ok) {
+          if (elect_one()) umma_commit(bar(C::B_KVFREE));  // K of this group is no longer read by dQ MMAs
           __syncwarp();
         }
       }
@@ -383,18 +414,18 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!ok) break;
           if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
           tc_fence_after_sync();
-          if ((warp & 3) == 0 && wh == 0) FTA_SSTAMP(4, tt + 16);
           const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + wh * 16;
           const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + wh * 16;
           const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1024) + wh * 16;
-          uint32_t dd[32];  // dS^T of this key row, 64 queries, packed 16-bit pairs
+          // ---- phase 1: P^T = exp2((S^T*scale + bias^T - max)*log2e - log2 sum), handed to the dV MMA.
+          // A half-precision copy of P (11 significant bits, more than the MMA operand keeps) stays
+          // in registers for phase 2.
+          uint32_t ph[32];
 #pragma unroll
           for (int cc = 0; cc < 2; ++cc) {
-            uint32_t sv[32], dv[32];
+            uint32_t sv[32];
             tmem_ld32(tST + cc * 32, sv);
-            tmem_ld32(tDP + cc * 32, dv);
             tmem_ld_wait();
-            if ((warp & 3) == 0 && wh == 0) FTA_SSTAMP(cc * 2, tt + 16);
             uint32_t pp[16];
 #pragma unroll
             for (int c8 = 0; c8 < 4; ++c8) {
@@ -402,14 +433,12 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
               const float4 ma = nm4[cc * 8 + c8 * 2], mb = nm4[cc * 8 + c8 * 2 + 1];
               const float4 la = nl4[cc * 8 + c8 * 2], lb = nl4[cc * 8 + c8 * 2 + 1];
-              const float4 da = del4[cc * 8 + c8 * 2], db = del4[cc * 8 + c8 * 2 + 1];
               const f32x2 nm2[4] = {mk2(ma.x, ma.y), mk2(ma.z, ma.w), mk2(mb.x, mb.y), mk2(mb.z, mb.w)};
               const f32x2 nl2[4] = {mk2(la.x, la.y), mk2(la.z, la.w), mk2(lb.x, lb.y), mk2(lb.z, lb.w)};
-              const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int idx = c8 * 8 + 2 * e;  // column within the 32-column chunk
-                float b0, b1, y0, y1, ds0, ds1;
+                float b0, b1, y0, y1;
                 unpack2<kBf16>(bw[e], b0, b1);
                 // x = s*scale + b exactly as the forward pass formed it; (x - max) is then exact
                 // for x near the max whatever its magnitude; y = (x - max)*log2e - log2(sum)
@@ -417,19 +446,45 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                      mk2(b0, b1));
                 un2(fma2(add2(x, nm2[e]), log2e2, nl2[e]), y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                pp[c8 * 4 + e] = pack2<kBf16>(p0, p1);
+                ph[cc * 16 + c8 * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[c8 * 4 + e];
+              }
+            }
+            tmem_st16(tST + cc * 16, pp);
+          }
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
+          if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
+          // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
+          ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
+          if (!ok) break;
+          tc_fence_after_sync();
+          uint32_t dd[32];  // dS^T of this key row, 64 queries, packed 16-bit pairs
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t dv[32];
+            tmem_ld32(tDP + cc * 32, dv);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+              const float4 da = del4[cc * 8 + c8 * 2], db = del4[cc * 8 + c8 * 2 + 1];
+              const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int idx = c8 * 8 + 2 * e;
+                float p0, p1, ds0, ds1;
+                unpack2<false>(ph[cc * 16 + c8 * 4 + e], p0, p1);
                 const f32x2 u = fma2(del2[e], neg1_2, mk2(__uint_as_float(dv[idx]), __uint_as_float(dv[idx + 1])));
                 const f32x2 ds = mul2(mk2(p0, p1), u);
                 acc[cc * 16 + c8 * 4 + e] = add2(acc[cc * 16 + c8 * 4 + e], ds);
                 un2(ds, ds0, ds1);
-                pp[c8 * 4 + e] = pack2<kBf16>(p0, p1);
                 dd[cc * 16 + c8 * 4 + e] = pack2<kBf16>(ds0, ds1);
               }
             }
-            tmem_st16(tST + cc * 16, pp);
             tmem_st16(tDP + cc * 16, dd + cc * 16);
-            if ((warp & 3) == 0 && wh == 0) FTA_SSTAMP(cc * 2 + 1, tt + 16);
           }
-          if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
             if (!ok) break;
@@ -444,7 +499,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           fence_proxy_async_smem();
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(C::B_PFULL + wh));
+          if (lane == 0) mbar_arrive(bar(C::B_P2FULL + wh));
           if ((warp & 3) == 0) FTA_STAMP(wh, 3, tt);
           if (wh == 1 && !(jb == 0 && g == 0)) {
             // dQ of the previous tile of this group is complete (DQDONE waited above)
@@ -486,6 +541,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       if (!ok) break;
       tc_fence_after_sync();
       if (wh == 1) {
+        ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
+        if (!ok) break;
+        tc_fence_after_sync();
         const int pt = nq * Gc - 1;
         reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
       }

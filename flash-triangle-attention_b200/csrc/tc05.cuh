@@ -88,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   for (uint32_t it = 0; it < (1u << 22); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*w.abort_flag) return false;
-    if (it > 64) __nanosleep(64);
+    if (it > 100000) __nanosleep(256);  // back off only when the wait is hopeless (try_wait itself suspends)
   }
   *w.abort_flag = 1;
   atomicCAS(w.status, kStatusOk, kStatusWaitTimeout | site);
