@@ -26,8 +26,8 @@
 //
 //   warp 0     : tcgen05 issuer (lowest warp id: the scheduler prefers older warps)
 //   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : idle
-//   warps 4-7  : compute warpgroup 0 (queries 0..63 of the tile)   also stores dV
-//   warps 8-11 : compute warpgroup 1 (queries 64..127)             also reduces dQ, stores dK
+//   warps 4-19 : four compute warpgroups, one 32-query quarter of the tile each; quarters 0-1
+//                (half 0) also store dV, quarters 2-3 (half 1) store dK, quarter 3 reduces dQ
 // Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
 #include "fta_kernels.h"
 #include "tc05.cuh"
@@ -36,6 +36,9 @@ namespace fta {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kBwdThreads = 640;    // 4 service warps + 16 compute warps
+constexpr int kAuxRegs = 56;        // registers per thread of the service warpgroup
+constexpr int kComputeRegs = 104;   // 512 * 104 + 128 * 56 <= 640 * 96, the CTA's register allotment at launch
 
 #ifdef FTA_TRACE
 // Debug build only: clock64() stamps of CTA 0, read back with fta_trace_read_bwd().
@@ -124,7 +127,7 @@ __device__ __forceinline__ void red_add(float* addr, float a) {
 }
 
 template <int kD, bool kBf16>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                const __grid_constant__ CUtensorMap tmBiasT, const BwdParams p) {
@@ -169,15 +172,15 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::B_BIASFULL + i), 1);
-      mbar_init(bar(C::B_BIASEMPTY + i), 8);
+      mbar_init(bar(C::B_BIASEMPTY + i), 16);  // one arrive per compute warp
       mbar_init(bar(C::B_SFULL + i), 1);
       mbar_init(bar(C::B_DPFULL + i), 1);
-      mbar_init(bar(C::B_P1FULL + i), 4);  // one arrive per warp of the warpgroup
-      mbar_init(bar(C::B_P2FULL + i), 4);
+      mbar_init(bar(C::B_P1FULL + i), 8);  // one arrive per warp of the two warpgroups of a half
+      mbar_init(bar(C::B_P2FULL + i), 8);
     }
     mbar_init(bar(C::B_DQDONE), 1);
     mbar_init(bar(C::B_ACCFULL), 1);
-    mbar_init(bar(C::B_ACCFREE), 8);
+    mbar_init(bar(C::B_ACCFREE), 16);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -190,7 +193,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const uint32_t tbase = *tmem_slot;
 
   if (warp < 4) {
-    reg_dec<88>();
+    reg_dec<kAuxRegs>();
     if (warp == 1) {
       // ---------------------------------------------------------------- TMA producer
       if (elect_one()) {
@@ -279,7 +282,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            umma_ts(td, ta + ks * 8, dB + ks * ((2 * C::SBO) >> 4), idesc_acc, ks > 0 ? 1u : acc_first);
+            umma_ts(td, ta + (ks >> 1) * 32 + (ks & 1) * 8, dB + ks * ((2 * C::SBO) >> 4), idesc_acc,
+                    ks > 0 ? 1u : acc_first);
         }
         __syncwarp();
       };
@@ -366,12 +370,17 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
-    reg_inc<208>();
-    const int wh = (warp >> 2) - 1;           // which 64-query half of the tile
-    const int key = (warp & 3) * 32 + lane;   // key row of the block == TMEM lane
+    // 16 warps = 4 warpgroups; warpgroup qd owns the 32-query quarter qd of the tile (half
+    // wh = qd / 2, chunk sub = qd % 2 of that half). Four compute warps per scheduler hide the
+    // ALU / MUFU / shared-memory latencies that two could not.
+    reg_inc<kComputeRegs>();
+    const int qd = (warp >> 2) - 1;
+    const int wh = qd >> 1, sub = qd & 1;
+    const int key = (warp & 3) * 32 + lane;  // key row of the block == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tST = tbase + C::TM_ST + wh * 64 + lane_off;
-    const uint32_t tDP = tbase + C::TM_DP + wh * 64 + lane_off;
+    // this quarter's 32 fp32 columns of S^T / dP^T; P^T / dS^T overwrite its first 16 columns
+    const uint32_t tST = tbase + C::TM_ST + wh * 64 + sub * 32 + lane_off;
+    const uint32_t tDP = tbase + C::TM_DP + wh * 64 + sub * 32 + lane_off;
     float* plane = p.planes + (static_cast<long long>(r) * p.BH + bh) * p.L2 * p.L2;
     const f32x2 scale2 = mk2(p.scale, p.scale);
     const f32x2 log2e2 = mk2(kLog2e, kLog2e);
@@ -396,48 +405,47 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const int i0 = (r + n * p.NP) * G;
       const int Gc = min(G, p.L1 - i0);
       for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
-        f32x2 acc[32];
+        f32x2 acc[16];  // dBias sums: this key column x 32 query rows
 #pragma unroll
-        for (int c = 0; c < 32; ++c) acc[c] = mk2(0.f, 0.f);
+        for (int c = 0; c < 16; ++c) acc[c] = mk2(0.f, 0.f);
         const int bs = nb & 1;
         ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
         if (!ok) break;
-        if ((warp & 3) == 0) FTA_STAMP(wh, 7, tt);
         const uint8_t* brow = sBias + bs * C::BIAS_B + wh * 16384 + key * 128;
         for (int g = 0; g < Gc; ++g, ++tt) {
           const int s = tt % C::NQ;
           const uint8_t* st = sQDO + s * C::STAGE_B;
-          if ((warp & 3) == 0) FTA_STAMP(wh, 0, tt);
+          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 0, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
-          ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // lse / delta visible
+          ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // statistics visible
           if (!ok) break;
-          if ((warp & 3) == 0) FTA_STAMP(wh, 1, tt);
+          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 1, tt);
           tc_fence_after_sync();
-          const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + wh * 16;
-          const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + wh * 16;
-          const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1024) + wh * 16;
+          const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + qd * 8;
+          const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + qd * 8;
+          const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1024) + qd * 8;
           // ---- phase 1: P^T = exp2((S^T*scale + bias^T - max)*log2e - log2 sum), handed to the dV MMA.
           // A half-precision copy of P (11 significant bits, more than the MMA operand keeps) stays
           // in registers for phase 2.
-          uint32_t ph[32];
+          uint32_t ph[16], pp[16];
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            uint32_t sv[32];
-            tmem_ld32(tST + cc * 32, sv);
+          for (int c16 = 0; c16 < 2; ++c16) {
+            uint32_t sv[16];
+            tmem_ld16(tST + c16 * 16, sv);
             tmem_ld_wait();
-            uint32_t pp[16];
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
-              const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((cc * 4 + c8) ^ (key & 7)) << 4));
+            for (int c8 = 0; c8 < 2; ++c8) {
+              const int ch = c16 * 2 + c8;  // 8-query chunk within the quarter
+              const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((sub * 4 + ch) ^ (key & 7)) << 4));
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-              const float4 ma = nm4[cc * 8 + c8 * 2], mb = nm4[cc * 8 + c8 * 2 + 1];
-              const float4 la = nl4[cc * 8 + c8 * 2], lb = nl4[cc * 8 + c8 * 2 + 1];
+              const float4 ma = nm4[ch * 2], mb = nm4[ch * 2 + 1];
+              const float4 la = nl4[ch * 2], lb = nl4[ch * 2 + 1];
               const f32x2 nm2[4] = {mk2(ma.x, ma.y), mk2(ma.z, ma.w), mk2(mb.x, mb.y), mk2(mb.z, mb.w)};
               const f32x2 nl2[4] = {mk2(la.x, la.y), mk2(la.z, la.w), mk2(lb.x, lb.y), mk2(lb.z, lb.w)};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int idx = c8 * 8 + 2 * e;  // column within the 32-column chunk
+                const int idx = c8 * 8 + 2 * e;  // column within the 16-column load
                 float b0, b1, y0, y1;
                 unpack2<kBf16>(bw[e], b0, b1);
                 // x = s*scale + b exactly as the forward pass formed it; (x - max) is then exact
@@ -446,79 +454,79 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                      mk2(b0, b1));
                 un2(fma2(add2(x, nm2[e]), log2e2, nl2[e]), y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-                pp[c8 * 4 + e] = pack2<kBf16>(p0, p1);
-                ph[cc * 16 + c8 * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[c8 * 4 + e];
+                pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
+                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
               }
             }
-            tmem_st16(tST + cc * 16, pp);
           }
+          tmem_st16(tST, pp);  // all 32 columns have been read: P^T goes over the first 16
           tmem_st_wait();
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
-          if ((warp & 3) == 0) FTA_STAMP(wh, 2, tt);
+          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 2, tt);
           // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
           ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
           if (!ok) break;
           tc_fence_after_sync();
-          uint32_t dd[32];  // dS^T of this key row, 64 queries, packed 16-bit pairs
+          uint32_t dd[16];  // dS^T of this key row, 32 queries, packed 16-bit pairs
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            uint32_t dv[32];
-            tmem_ld32(tDP + cc * 32, dv);
+          for (int c16 = 0; c16 < 2; ++c16) {
+            uint32_t dv[16];
+            tmem_ld16(tDP + c16 * 16, dv);
             tmem_ld_wait();
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
-              const float4 da = del4[cc * 8 + c8 * 2], db = del4[cc * 8 + c8 * 2 + 1];
+            for (int c8 = 0; c8 < 2; ++c8) {
+              const int ch = c16 * 2 + c8;
+              const float4 da = del4[ch * 2], db = del4[ch * 2 + 1];
               const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int idx = c8 * 8 + 2 * e;
                 float p0, p1, ds0, ds1;
-                unpack2<false>(ph[cc * 16 + c8 * 4 + e], p0, p1);
+                unpack2<false>(ph[ch * 4 + e], p0, p1);
                 const f32x2 u = fma2(del2[e], neg1_2, mk2(__uint_as_float(dv[idx]), __uint_as_float(dv[idx + 1])));
                 const f32x2 ds = mul2(mk2(p0, p1), u);
-                acc[cc * 16 + c8 * 4 + e] = add2(acc[cc * 16 + c8 * 4 + e], ds);
+                acc[ch * 4 + e] = add2(acc[ch * 4 + e], ds);
                 un2(ds, ds0, ds1);
-                dd[cc * 16 + c8 * 4 + e] = pack2<kBf16>(ds0, ds1);
+                dd[ch * 4 + e] = pack2<kBf16>(ds0, ds1);
               }
             }
-            tmem_st16(tDP + cc * 16, dd + cc * 16);
           }
+          tmem_st16(tDP, dd);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
             if (!ok) break;
           }
           // dS^T row of this key into the M-major staging tile (128-byte swizzle)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < 4; ++j) {
             const uint4 v4 = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
-            *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + ((j ^ (key & 7)) << 4)) = v4;
+            *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + (((sub * 4 + j) ^ (key & 7)) << 4)) = v4;
           }
           tmem_st_wait();
           fence_proxy_async_smem();
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_P2FULL + wh));
-          if ((warp & 3) == 0) FTA_STAMP(wh, 3, tt);
-          if (wh == 1 && !(jb == 0 && g == 0)) {
+          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 3, tt);
+          if (qd == 3 && !(jb == 0 && g == 0)) {
             // dQ of the previous tile of this group is complete (DQDONE waited above)
             const int pt = jb * Gc + g - 1;
             tc_fence_after_sync();
             reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
           }
-          if ((warp & 3) == 0) FTA_STAMP(wh, 4, tt);
+          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 4, tt);
         }
         if (!ok) break;
-        if ((warp & 3) == 0) FTA_STAMP(wh, 5, tt - 1);
         // bias stage no longer needed by this warp
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
         // dBias: add this CTA's sums over the G rows to its private plane
-        float* dst = plane + (static_cast<long long>(jb) * 128 + wh * 64) * p.L2 + kb * 128 + key;
+        float* dst = plane + (static_cast<long long>(jb) * 128 + qd * 32) * p.L2 + kb * 128 + key;
         if (n == 0) {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
+          for (int c = 0; c < 16; ++c) {
             float a0, a1;
             un2(acc[c], a0, a1);
             dst[static_cast<long long>(2 * c) * p.L2] = a0;
@@ -526,21 +534,20 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
+          for (int c = 0; c < 16; ++c) {
             float a0, a1;
             un2(acc[c], a0, a1);
             red_add(dst + static_cast<long long>(2 * c) * p.L2, a0);
             red_add(dst + static_cast<long long>(2 * c + 1) * p.L2, a1);
           }
         }
-        if ((warp & 3) == 0) FTA_STAMP(wh, 6, tt - 1);
       }
       if (!ok) break;
       // ---- group epilogue: last dQ tile, then dK / dV of the G rows
       ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
       if (!ok) break;
       tc_fence_after_sync();
-      if (wh == 1) {
+      if (qd == 3) {
         ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
         if (!ok) break;
         tc_fence_after_sync();
@@ -548,12 +555,13 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
       }
       {
-        // warpgroup 0 stores dV, warpgroup 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518)
+        // half 0 stores dV, half 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518); the two
+        // warpgroups of a half take alternate rows of the group
         const long long* sd = (wh == 0) ? p.sdv : p.sdk;
         uint16_t* base = reinterpret_cast<uint16_t*>(wh == 0 ? p.dv : p.dk) + b * sd[0] + h * sd[1] +
                          static_cast<long long>(kb * 128 + key) * sd[3];
         const float mul = (wh == 0) ? 1.0f : p.scale;
-        for (int g = 0; g < Gc; ++g) {
+        for (int g = sub; g < Gc; g += 2) {
           uint16_t* optr = base + static_cast<long long>(i0 + g) * sd[2];
           const uint32_t ta = tbase + C::TM_ACC + g * 2 * kD + (wh == 0 ? kD : 0) + lane_off;
 #pragma unroll
@@ -620,7 +628,7 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   p.scale = a.sm_scale;
   p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
   const int grid = a.B * a.H * NP * (a.L2 / 128);
-  kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, p);
+  kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

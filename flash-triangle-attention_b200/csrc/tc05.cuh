@@ -79,16 +79,28 @@ struct WaitCtx {
   int* status;               // global memory, one per launch
 };
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 // Bounded wait on an mbarrier phase. Returns false when the wait ran out or another role
 // already aborted; the caller must then skip to the tear-down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int site) {
   // fast path
   if (mbar_try_wait(bar, parity)) return true;
-  // ~ (1<<22) polls with a short back-off: of the order of a second at worst.
-  for (uint32_t it = 0; it < (1u << 22); ++it) {
+  // Spin on try_wait (which itself suspends the thread for a short, bounded time). The wait
+  // gives up after about a second of wall-clock time, measured with the global nanosecond timer.
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0; it < (1u << 30); ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*w.abort_flag) return false;
-    if (it > 100000) __nanosleep(256);  // back off only when the wait is hopeless (try_wait itself suspends)
+    if ((it & 0x3ff) == 0x3ff) {
+      const unsigned long long now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 1000000000ull) break;
+    }
   }
   *w.abort_flag = 1;
   atomicCAS(w.status, kStatusOk, kStatusWaitTimeout | site);
