@@ -188,7 +188,7 @@ def main():
     B, H, L2, D = w.B, w.H, w.L2, w.D
     prob = FtaProblem(B, H, nrows, L2, D, _cabi.FTA_BF16)
     o = torch.empty_like(d["q"])
-    lse = torch.empty(2, B, H, nrows, L2, dtype=torch.float32, device=dev)
+    lse = torch.empty(3, B, H, nrows, L2, dtype=torch.float32, device=dev)
     delta = torch.empty(B, H, nrows, L2, dtype=torch.float32, device=dev)
     dq, dk, dv = (torch.empty_like(d["q"]) for _ in range(3))
     db = torch.empty_like(d["bias"])

@@ -63,7 +63,7 @@ struct BwdCfg {
   static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + 2*D + 2*D*G <= 512)
   static constexpr int NQ = (kD == 32) ? 4 : 2;  // Q/dO ring depth
   static constexpr int TILE_B = 128 * kD * 2;
-  static constexpr int STAGE_B = 2 * TILE_B + 2048;  // Q, dO, -max[128], -log2sum[128], delta[128], pad
+  static constexpr int STAGE_B = 2 * TILE_B + 2048;  // Q, dO, -max[128], -log2sum[128], delta[128], c[128]
   static constexpr int BIAS_B = 128 * 128 * 2;
   static constexpr int DS_B = 128 * 128 * 2;
   static constexpr int OFF_KV = 0;
@@ -98,7 +98,7 @@ struct BwdCfg {
 };
 
 struct BwdParams {
-  const float* lse;  // two planes: -max (natural-log units), -log2(sum)
+  const float* lse;  // three planes: -max (natural-log units), -log2(sum), c (see the forward kernel)
   const float* delta;
   float* dq32;
   void* dk;
@@ -108,7 +108,7 @@ struct BwdParams {
   int H, L1, L2, NP, BH;
   long long sdk[4], sdv[4];
   float scale;  // sm_scale
-  long long stat_stride;  // elements between the two statistics planes
+  long long stat_stride;  // elements between the statistics planes
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -236,7 +236,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (!ok) break;
             if (elect_one()) {
               uint8_t* st = sQDO + s * C::STAGE_B;
-              mbar_expect_tx(bar(C::B_QDOFULL + s), 2 * C::TILE_B + 1536);
+              mbar_expect_tx(bar(C::B_QDOFULL + s), 2 * C::TILE_B + 2048);
               tma_load_5d(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
               tma_load_5d(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
               const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
@@ -244,6 +244,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.lse + p.stat_stride + roff, 512,
                            bar(C::B_QDOFULL + s));
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 1024), p.delta + roff, 512, bar(C::B_QDOFULL + s));
+              bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 1536), p.lse + 2 * p.stat_stride + roff, 512,
+                           bar(C::B_QDOFULL + s));
             }
           }
         }
@@ -384,6 +386,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     float* plane = p.planes + (static_cast<long long>(r) * p.BH + bh) * p.L2 * p.L2;
     const f32x2 scale2 = mk2(p.scale, p.scale);
     const f32x2 log2e2 = mk2(kLog2e, kLog2e);
+    const f32x2 k1_2 = mk2(p.scale * kLog2e, p.scale * kLog2e);
     const f32x2 neg1_2 = mk2(-1.f, -1.f);
     bool ok = true;
     int tt = 0, nb = 0;
@@ -429,6 +432,39 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           // A half-precision copy of P (11 significant bits, more than the MMA operand keeps) stays
           // in registers for phase 2.
           uint32_t ph[16], pp[16];
+          const float4* c4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1536) + qd * 8;
+          // one lane per query of the quarter looks at c: NaN = a row that needs the two-part form
+          const float cq = reinterpret_cast<const float*>(st + 2 * C::TILE_B + 1536)[qd * 32 + lane];
+          const bool robust = __any_sync(0xffffffffu, cq != cq);
+          if (!robust) {
+            // y = s*scale*log2e + b*log2e + c
+#pragma unroll
+            for (int c16 = 0; c16 < 2; ++c16) {
+              uint32_t sv[16];
+              tmem_ld16(tST + c16 * 16, sv);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c8 = 0; c8 < 2; ++c8) {
+                const int ch = c16 * 2 + c8;  // 8-query chunk within the quarter
+                const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((sub * 4 + ch) ^ (key & 7)) << 4));
+                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+                const float4 ca = c4[ch * 2], cb = c4[ch * 2 + 1];
+                const f32x2 c2[4] = {mk2(ca.x, ca.y), mk2(ca.z, ca.w), mk2(cb.x, cb.y), mk2(cb.z, cb.w)};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int idx = c8 * 8 + 2 * e;  // column within the 16-column load
+                  float b0, b1, y0, y1;
+                  unpack2<kBf16>(bw[e], b0, b1);
+                  un2(fma2(mk2(__uint_as_float(sv[idx]), __uint_as_float(sv[idx + 1])), k1_2,
+                           fma2(mk2(b0, b1), log2e2, c2[e])),
+                      y0, y1);
+                  const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                  pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
+                  ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                }
+              }
+            }
+          } else {
 #pragma unroll
           for (int c16 = 0; c16 < 2; ++c16) {
             uint32_t sv[16];
@@ -458,6 +494,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
               }
             }
+          }
           }
           tmem_st16(tST, pp);  // all 32 columns have been read: P^T goes over the first 16
           tmem_st_wait();

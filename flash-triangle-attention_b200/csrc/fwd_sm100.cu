@@ -405,8 +405,14 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // softmax statistics for the backward pass: -max (natural-log units) and -log2(sum).
             // Kept apart: their sum in one float would lose log2(sum) when |max| is huge.
             const long long ridx = (static_cast<long long>(bh) * p.L1 + i) * p.L2 + j;
+            const float nl = -log2f(l_new);
             p.lse[ridx] = -m_safe;
-            p.lse[p.stat_stride + ridx] = -log2f(l_new);
+            p.lse[p.stat_stride + ridx] = nl;
+            // plane 2: both in one number, c = -(max*log2e + log2 sum), for rows where that loses
+            // nothing; NaN marks rows whose max is so large (fully masked rows) that the
+            // backward pass must use the two parts separately
+            p.lse[2 * p.stat_stride + ridx] =
+                (fabsf(m_safe) > 1.0e4f) ? __int_as_float(0x7fc00000) : fmaf(-m_safe, kLog2e, nl);
           }
         }
       }

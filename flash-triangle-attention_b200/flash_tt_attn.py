@@ -91,7 +91,7 @@ class _attention(torch.autograd.Function):
 
         q, k, v, b_pw = _dense(q), _dense(k), _dense(v), _dense(b_pw)
         o = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=q.device)
-        lse = torch.empty((2, B, H, L1, L2), dtype=torch.float32, device=q.device)  # softmax statistics
+        lse = torch.empty((3, B, H, L1, L2), dtype=torch.float32, device=q.device)  # softmax statistics
         status = _status(q.device)
         prob = _problem(q)
         with torch.cuda.device(q.device):

@@ -24,7 +24,7 @@ def _setup():
     prob = FtaProblem(B, H, L1, L2, D, _cabi.FTA_BF16)
     L = _cabi.lib()
     o = torch.empty_like(d["q"])
-    lse = torch.empty(2, B, H, L1, L2, dtype=torch.float32, device="cuda")
+    lse = torch.empty(3, B, H, L1, L2, dtype=torch.float32, device="cuda")
     delta = torch.empty(B, H, L1, L2, dtype=torch.float32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
