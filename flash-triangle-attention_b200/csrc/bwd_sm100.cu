@@ -681,26 +681,26 @@ int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
 
 // Number of private dBias planes == number of row-group residue classes. Chosen so that the
 // grid (B*H * L2/128 * NP CTAs, one per SM at a time) fills whole waves of the device with
-// chains of nearly equal length.
+// chains of nearly equal length, with as few planes as that allows.
 int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms) {
   const int G = bwd_rows_per_cta(D);
   const int ngroups = (L1 + G - 1) / G;
   const long long base = static_cast<long long>(B) * H * (L2 / 128);
-  int best = 1;
-  double best_eff = -1.0;
   const int np_max = ngroups < 64 ? ngroups : 64;
-  for (int np = 1; np <= np_max; ++np) {
+  auto efficiency = [&](int np) {
     const long long ctas = base * np;
     const long long waves = (ctas + num_sms - 1) / num_sms;
     const int chain = (ngroups + np - 1) / np;  // longest chain
     // time ~ waves * chain ; work ~ base * ngroups / num_sms
-    const double eff = (static_cast<double>(base) * ngroups / num_sms) / (static_cast<double>(waves) * chain);
-    if (eff > best_eff + 1e-9) {
-      best_eff = eff;
-      best = np;
-    }
-  }
-  return best;
+    return (static_cast<double>(base) * ngroups / num_sms) / (static_cast<double>(waves) * chain);
+  };
+  double best_eff = -1.0;
+  for (int np = 1; np <= np_max; ++np) best_eff = efficiency(np) > best_eff ? efficiency(np) : best_eff;
+  // The planes are updated in place all through the kernel, so their footprint should stay
+  // inside the L2 cache: take the FEWEST planes whose schedule is within 7 % of the best one.
+  for (int np = 1; np <= np_max; ++np)
+    if (efficiency(np) >= 0.93 * best_eff) return np;
+  return 1;
 }
 
 int launch_bwd(const BwdArgs& a, cudaStream_t stream) {

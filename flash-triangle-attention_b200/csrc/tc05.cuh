@@ -73,6 +73,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// Same with a suspend-time hint: the hardware may park the thread for up to `hint_ns` and
+// wakes it when the phase completes, so a waiting warp does not burn issue slots polling.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
+
 // Shared abort flag + global status word, carried by every role.
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory, one per CTA
@@ -94,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   // gives up after about a second of wall-clock time, measured with the global nanosecond timer.
   unsigned long long t0 = 0;
   for (uint32_t it = 0; it < (1u << 30); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
     if (*w.abort_flag) return false;
     if ((it & 0x3ff) == 0x3ff) {
       const unsigned long long now = global_timer_ns();
