@@ -27,7 +27,7 @@
 //   warp 0     : tcgen05 issuer (lowest warp id: the scheduler prefers older warps)
 //   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : idle
 //   warps 4-19 : four compute warpgroups, one 32-query quarter of the tile each; quarters 0-1
-//                (half 0) also store dV, quarters 2-3 (half 1) store dK, quarter 3 reduces dQ
+//                (half 0) also store dV, quarters 2-3 (half 1) store dK; each reduces a quarter of dQ
 // Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
 #include "fta_kernels.h"
 #include "tc05.cuh"
@@ -390,18 +390,20 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const f32x2 neg1_2 = mk2(-1.f, -1.f);
     bool ok = true;
     int tt = 0, nb = 0;
-    // reduce one finished dQ tile (TMEM buffer `buf`) into the float32 dQ accumulator
+    // reduce this warpgroup's quarter of the columns of one finished dQ tile (TMEM buffer `buf`)
+    // into the float32 dQ accumulator; the four warpgroups share the work evenly
     auto reduce_dq = [&](int buf, int irow, int jblk) {
-      float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128 + key) * kD;
+      constexpr int W = kD / 4;  // columns per warpgroup
+      float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128 + key) * kD + qd * W;
 #pragma unroll
-      for (int c = 0; c < kD / 32; ++c) {
-        uint32_t qv[32];
-        tmem_ld32(tbase + C::TM_DQ + buf * kD + c * 32 + lane_off, qv);
+      for (int c = 0; c < W / 8; ++c) {
+        uint32_t qv[8];
+        tmem_ld8(tbase + C::TM_DQ + buf * kD + qd * W + c * 8 + lane_off, qv);
         tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          red_add_v4(dst + c * 32 + j * 4, __uint_as_float(qv[4 * j]), __uint_as_float(qv[4 * j + 1]),
-                     __uint_as_float(qv[4 * j + 2]), __uint_as_float(qv[4 * j + 3]));
+        red_add_v4(dst + c * 8, __uint_as_float(qv[0]), __uint_as_float(qv[1]), __uint_as_float(qv[2]),
+                   __uint_as_float(qv[3]));
+        red_add_v4(dst + c * 8 + 4, __uint_as_float(qv[4]), __uint_as_float(qv[5]), __uint_as_float(qv[6]),
+                   __uint_as_float(qv[7]));
       }
     };
     for (int n = 0; n < ngroups && ok; ++n) {
@@ -547,7 +549,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_P2FULL + wh));
           if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 3, tt);
-          if (qd == 3 && !(jb == 0 && g == 0)) {
+          if (!(jb == 0 && g == 0)) {
             // dQ of the previous tile of this group is complete (DQDONE waited above)
             const int pt = jb * Gc + g - 1;
             tc_fence_after_sync();
@@ -584,7 +586,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
       if (!ok) break;
       tc_fence_after_sync();
-      if (qd == 3) {
+      {
         ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
         if (!ok) break;
         tc_fence_after_sync();
