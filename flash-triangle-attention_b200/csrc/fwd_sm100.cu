@@ -59,7 +59,8 @@ struct FwdCfg {
   static constexpr int OFF_BAR = OFF_BIAS + 2 * BIAS_B;
   // barrier slots
   static constexpr int B_QFULL = 0;
-  static constexpr int B_KVFULL = B_QFULL + G;
+  static constexpr int B_QEMPTY = B_QFULL + G;
+  static constexpr int B_KVFULL = B_QEMPTY + G;
   static constexpr int B_KVEMPTY = B_KVFULL + NSTAGE;
   static constexpr int B_BIASFULL = B_KVEMPTY + NSTAGE;
   static constexpr int B_BIASEMPTY = B_BIASFULL + 2;
@@ -119,18 +120,25 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jb = blockIdx.x, ig = blockIdx.y, bh = blockIdx.z;
+  const int jb = blockIdx.x, bh = blockIdx.z;
   const int b = bh / p.H, h = bh % p.H;
-  const int i0 = ig * G;
-  const int Gc = min(G, p.L1 - i0);
-  const int Gp = (Gc + 1) & ~1;  // rows processed (an odd tail is padded with a zero row)
   const int nkb = p.L2 / 128;
-  const int T = nkb * Gp;
+  // This CTA walks the row groups blockIdx.y, blockIdx.y + gridDim.y, ... ("units") back to back;
+  // loads and MMAs of the next unit start while the softmax warps finish the current one.
+  const int ngroups = (p.L1 + G - 1) / G;
+  const int nunits = (ngroups - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) /
+                     static_cast<int>(gridDim.y);
+  auto unit_i0 = [&](int u) { return (static_cast<int>(blockIdx.y) + u * static_cast<int>(gridDim.y)) * G; };
+  // rows processed in a unit (an odd tail is padded with a zero row)
+  auto unit_gp = [&](int u) { return (min(G, p.L1 - unit_i0(u)) + 1) & ~1; };
   const WaitCtx w{abort_flag, p.status};
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < G; ++i) mbar_init(bar(C::B_QFULL + i), 1);
+    for (int i = 0; i < G; ++i) {
+      mbar_init(bar(C::B_QFULL + i), 1);
+      mbar_init(bar(C::B_QEMPTY + i), 1);
+    }
     for (int i = 0; i < C::NSTAGE; ++i) {
       mbar_init(bar(C::B_KVFULL + i), 1);
       mbar_init(bar(C::B_KVEMPTY + i), 1);
@@ -165,33 +173,41 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_prefetch_desc(&tmBias);
       }
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int bs = kb & 1;
-        ok = mbar_wait_warp(bar(C::B_BIASEMPTY + bs), ((kb >> 1) & 1) ^ 1, w, 1);
-        if (!ok) break;
-        if (elect_one()) {
-          mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
-          tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128,
-                      jb * 128, h, b);
-          tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBias, bar(C::B_BIASFULL + bs),
-                      kb * 128 + 64, jb * 128, h, b);
-        }
-        for (int g = 0; g < Gp; ++g) {
-          if (kb == 0 && elect_one()) {
-            mbar_expect_tx(bar(C::B_QFULL + g), C::TILE_B);
-            tma_load_5d(smem_u32(sQ + g * C::TILE_B), &tmQ, bar(C::B_QFULL + g), 0, jb * 128, i0 + g,
-                        h, b);
-          }
-          const int t = kb * Gp + g;
-          const int s = t % C::NSTAGE;
-          ok = mbar_wait_warp(bar(C::B_KVEMPTY + s), ((t / C::NSTAGE) & 1) ^ 1, w, 2);
+      int tt = 0, nbias = 0;
+      for (int u = 0; u < nunits && ok; ++u) {
+        const int i0 = unit_i0(u), Gp = unit_gp(u);
+        for (int kb = 0; kb < nkb && ok; ++kb, ++nbias) {
+          const int bs = nbias & 1;
+          ok = mbar_wait_warp(bar(C::B_BIASEMPTY + bs), ((nbias >> 1) & 1) ^ 1, w, 1);
           if (!ok) break;
           if (elect_one()) {
-            mbar_expect_tx(bar(C::B_KVFULL + s), 2 * C::TILE_B);
-            tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL + s), 0, kb * 128,
-                        i0 + g, h, b);
-            tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL + s), 0,
-                        kb * 128, i0 + g, h, b);
+            mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
+            tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBias, bar(C::B_BIASFULL + bs), kb * 128,
+                        jb * 128, h, b);
+            tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBias, bar(C::B_BIASFULL + bs),
+                        kb * 128 + 64, jb * 128, h, b);
+          }
+          for (int g = 0; g < Gp; ++g, ++tt) {
+            if (kb == 0) {
+              // the Q tile of this row slot is free once the last Q K^T of the previous unit is done
+              ok = mbar_wait_warp(bar(C::B_QEMPTY + g), (u & 1) ^ 1, w, 11);
+              if (!ok) break;
+              if (elect_one()) {
+                mbar_expect_tx(bar(C::B_QFULL + g), C::TILE_B);
+                tma_load_5d(smem_u32(sQ + g * C::TILE_B), &tmQ, bar(C::B_QFULL + g), 0, jb * 128, i0 + g,
+                            h, b);
+              }
+            }
+            const int s = tt % C::NSTAGE;
+            ok = mbar_wait_warp(bar(C::B_KVEMPTY + s), ((tt / C::NSTAGE) & 1) ^ 1, w, 2);
+            if (!ok) break;
+            if (elect_one()) {
+              mbar_expect_tx(bar(C::B_KVFULL + s), 2 * C::TILE_B);
+              tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL + s), 0, kb * 128,
+                          i0 + g, h, b);
+              tma_load_5d(smem_u32(sKV + s * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL + s), 0,
+                          kb * 128, i0 + g, h, b);
+            }
           }
         }
       }
@@ -201,13 +217,27 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       constexpr uint32_t idesc_pv = umma_idesc_f16(kBf16 ? 1 : 0, 128, kD, 0, 1);
       const uint32_t sQ_a = smem_u32(sQ), sKV_a = smem_u32(sKV);
       bool ok = true;
-      // S(t) = Q_g K^T into S buffer g&1, once the buffer's previous tile has been copied
-      // out by its warpgroup.
-      auto issue_qk = [&](int t) -> bool {
-        const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE, wb = g & 1;
-        const int n = kb * (Gp >> 1) + (g >> 1);  // tile index within this S buffer
-        if (kb == 0 && !mbar_wait_warp(bar(C::B_QFULL + g), 0, w, 3)) return false;
-        if (!mbar_wait_warp(bar(C::B_KVFULL + s), (t / C::NSTAGE) & 1, w, 4)) return false;
+      // the tile sequence (unit, key block, row) flattened; `tt` = global tile index
+      struct TileIt { int u, kb, g, gp, tt; };
+      auto it_valid = [&](const TileIt& it) { return it.u < nunits; };
+      auto it_next = [&](TileIt& it) {
+        ++it.tt;
+        if (++it.g == it.gp) {
+          it.g = 0;
+          if (++it.kb == nkb) {
+            it.kb = 0;
+            if (++it.u < nunits) it.gp = unit_gp(it.u);
+          }
+        }
+      };
+      int nqk[2] = {0, 0}, npv[2] = {0, 0};  // tiles issued per S / P buffer
+      // S = Q_g K^T into S buffer g&1, once the buffer's previous tile has been copied out by its
+      // warpgroup.
+      auto issue_qk = [&](const TileIt& it) -> bool {
+        const int g = it.g, s = it.tt % C::NSTAGE, wb = g & 1;
+        const int n = nqk[wb];
+        if (it.kb == 0 && !mbar_wait_warp(bar(C::B_QFULL + g), it.u & 1, w, 3)) return false;
+        if (!mbar_wait_warp(bar(C::B_KVFULL + s), (it.tt / C::NSTAGE) & 1, w, 4)) return false;
         if (n > 0 && !mbar_wait_warp(bar(C::B_SFREE + wb), (n - 1) & 1, w, 9)) return false;
         tc_fence_after_sync();
         const uint64_t dq = umma_smem_desc(sQ_a + g * C::TILE_B, 16, C::SBO, C::SWZ);
@@ -217,34 +247,44 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           for (int ks = 0; ks < kD / 16; ++ks)
             umma_ss(tbase + wb * 128, dq + ks * 2, dk + ks * 2, idesc_qk, ks > 0);
           umma_commit(bar(C::B_SFULL + wb));
+          if (it.kb == nkb - 1) umma_commit(bar(C::B_QEMPTY + g));  // last use of this unit's Q tile
         }
         __syncwarp();
+        ++nqk[wb];
         return true;
       };
-      ok = issue_qk(0) && issue_qk(1);
-      for (int t = 0; t < T && ok; ++t) {
-        const int g = t % Gp, kb = t / Gp, s = t % C::NSTAGE, wb = g & 1;
-        const int n = kb * (Gp >> 1) + (g >> 1);
-        if (t + 2 < T) {
-          ok = issue_qk(t + 2);  // waits until S(t) has been copied out
+      TileIt cur{0, 0, 0, nunits > 0 ? unit_gp(0) : 2, 0};
+      TileIt ahead = cur;
+      for (int k = 0; k < 2 && ok && it_valid(ahead); ++k) {
+        ok = issue_qk(ahead);
+        it_next(ahead);
+      }
+      while (ok && it_valid(cur)) {
+        const int g = cur.g, s = cur.tt % C::NSTAGE, wb = g & 1;
+        if (it_valid(ahead)) {
+          ok = issue_qk(ahead);  // waits until the S tile two tiles back has been copied out
           if (!ok) break;
+          it_next(ahead);
         }
-        FTA_STAMP(2, 0, t);
-        ok = mbar_wait_warp(bar(C::B_PFULL + wb), n & 1, w, 5);
+        FTA_STAMP(2, 0, cur.tt);
+        ok = mbar_wait_warp(bar(C::B_PFULL + wb), npv[wb] & 1, w, 5);
         if (!ok) break;
-        FTA_STAMP(2, 1, t);
+        FTA_STAMP(2, 1, cur.tt);
         tc_fence_after_sync();
         const uint64_t dv = umma_smem_desc(sKV_a + s * 2 * C::TILE_B + C::TILE_B, C::SBO, C::SBO, C::SWZ);
+        const uint32_t acc0 = cur.kb > 0 ? 1u : 0u;
         if (elect_one()) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)
             umma_ts(tbase + C::TMEM_O + g * kD, tbase + C::TMEM_P + wb * 64 + ks * 8,
-                    dv + ks * ((2 * C::SBO) >> 4), idesc_pv, (kb > 0 || ks > 0) ? 1u : 0u);
+                    dv + ks * ((2 * C::SBO) >> 4), idesc_pv, ks > 0 ? 1u : acc0);
           umma_commit(bar(C::B_KVEMPTY + s));
           umma_commit(bar(C::B_PVDONE + wb));
         }
         __syncwarp();
-        FTA_STAMP(2, 2, t);
+        FTA_STAMP(2, 2, cur.tt);
+        ++npv[wb];
+        it_next(cur);
       }
     }
   } else {
@@ -257,17 +297,19 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t tP = tbase + C::TMEM_P + wg * 64 + lane_off;
     const f32x2 scale2 = mk2(p.scale, p.scale);
     const f32x2 log2e2 = mk2(kLog2e, kLog2e);
+    int n = 0, nbias = 0;
+    bool ok = true;
+    for (int u = 0; u < nunits && ok; ++u) {
+    const int i0 = unit_i0(u);
+    const int ngi = unit_gp(u) >> 1;
     float m_used[G / 2], l_run[G / 2];  // running max (natural-log units) and running sum
 #pragma unroll
     for (int i = 0; i < G / 2; ++i) {
       m_used[i] = -INFINITY;
       l_run[i] = 0.f;
     }
-    const int ngi = Gp >> 1;
-    int n = 0;
-    bool ok = true;
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      const int bs = kb & 1;
+    for (int kb = 0; kb < nkb && ok; ++kb, ++nbias) {
+      const int bs = nbias & 1;
       const uint8_t* brow = sBias + bs * C::BIAS_B + row * 128;
       for (int gi = 0; gi < ngi; ++gi, ++n) {
         const int g = 2 * gi + wg;
@@ -275,7 +317,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ok = mbar_wait_warp(bar(C::B_SFULL + wg), n & 1, w, 6);
         if (!ok) break;
         if (gi == 0) {
-          ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (kb >> 1) & 1, w, 7);
+          ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nbias >> 1) & 1, w, 7);
           if (!ok) break;
         }
         if ((warp & 3) == 0) FTA_STAMP(wg, 1, n);
@@ -417,6 +459,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
       }
     }
+    }  // units
   }
 
   // ---------------------------------------------------------------------- tear-down
@@ -450,7 +493,41 @@ int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   p.so_j = a.so[3];
   p.scale = a.sm_scale;
   p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
-  dim3 grid(a.L2 / 128, (a.L1 + C::G - 1) / C::G, a.B * a.H);
+  // Row groups are dealt round-robin to grid.y CTAs per (query block, head). Pick the smallest
+  // grid.y whose schedule (waves of one CTA per SM, the longest CTA setting the pace) is within
+  // 3 % of the best: few long-lived CTAs amortise their start-up and keep the pipeline full
+  // across row groups.
+  const int ngroups = (a.L1 + C::G - 1) / C::G;
+  const long long per = static_cast<long long>(a.L2 / 128) * a.B * a.H;
+  int sms = 148;
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int best_gy = 1;
+  {
+    double best = 0.0;
+    const int gy_max = ngroups;
+    // first pass: best efficiency; second: smallest gy close to it
+    for (int pass = 0; pass < 2; ++pass) {
+      for (int gy = 1; gy <= gy_max; ++gy) {
+        const long long ctas = per * gy;
+        const long long waves = (ctas + sms - 1) / sms;
+        const int longest = (ngroups + gy - 1) / gy;
+        // fixed cost per CTA of about a third of a row group
+        const double eff = static_cast<double>(per) * ngroups /
+                           (static_cast<double>(waves) * sms * (longest + 0.35));
+        if (pass == 0) {
+          if (eff > best) best = eff;
+        } else if (eff >= 0.97 * best) {
+          best_gy = gy;
+          break;
+        }
+      }
+    }
+  }
+  dim3 grid(a.L2 / 128, best_gy, a.B * a.H);
   kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmBias, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
