@@ -85,11 +85,13 @@ FTA_API int fta_last_cuda_error(void);
 /* Forward pass. Replaces the `_attn_fwd` launch of `_attention.forward`
  * (flash_tt_attn.py:556-593, kernel 128-264): writes O (same dtype as q) and the softmax
  * statistics of every query row for the backward pass, `lse`, float32 contiguous of shape
- * (2,B,H,L1,L2): plane 0 holds -max_k(S) in natural-log units, plane 1 holds
+ * (3,B,H,L1,L2): plane 0 holds -max_k(S) in natural-log units, plane 1 holds
  * -log2(sum_k exp(S - max)). The reference saves their combination, the base-2
  * log-sum-exp max*log2(e) + log2(sum) (flash_tt_attn.py:258-263) = -(plane0*log2(e) + plane1);
  * the two parts are kept apart here because their float32 sum loses log2(sum) when a row is
- * fully masked with a large negative bias (|max| ~ 1e9).
+ * fully masked with a large negative bias (|max| ~ 1e9). Plane 2 holds that combination,
+ * plane0*log2(e) + plane1, for rows with |max| <= 1e4 (the backward pass then needs one
+ * statistic per row) and NaN for the others (the backward pass uses planes 0 and 1).
  * `status` points to one int32 the caller zeroed. */
 FTA_API int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
                 const FtaTensor5* v, const FtaTensor4* bias, float sm_scale,
@@ -109,7 +111,7 @@ FTA_API size_t fta_bwd_workspace_bytes(const FtaProblem* prob);
 FTA_API int fta_bwd_num_planes(const FtaProblem* prob);
 
 /* Backward pass. Replaces the `_attn_bwd` launch and the `zeros_like` dBias buffer of
- * `_attention.backward` (flash_tt_attn.py:596-660, kernel 442-550). Needs `lse` (both planes) from
+ * `_attention.backward` (flash_tt_attn.py:596-660, kernel 442-550). Needs `lse` (all three planes) from
  * fta_forward and `delta` from fta_bwd_preprocess. Writes dq, dk, dv (dtype of q), the
  * float32 dBias `dbias_f32` (B,H,L2,L2 contiguous; the sum over this call's L1 rows, in a
  * fixed order, so bit-reproducible) and, when `dbias_cast` is not NULL, the same rounded to
