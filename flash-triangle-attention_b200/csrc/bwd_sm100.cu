@@ -134,8 +134,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   using C = BwdCfg<kD>;
   constexpr int G = C::G;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // 1 KB alignment by an offset from the shared array itself, so that the compiler keeps the
+  // shared address space (ld.shared / st.shared instead of generic accesses)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sKV = smem + C::OFF_KV;    // [g][K tile | V tile]
   uint8_t* sQDO = smem + C::OFF_QDO;  // [stage][Q | dO | lse | delta]
   uint8_t* sBias = smem + C::OFF_BIAS;  // [stage][query half][key row][64 queries], 128B swizzle
@@ -157,7 +158,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int b = bh / p.H, h = bh % p.H;
   const int ngroups_total = (p.L1 + G - 1) / G;
   const int ngroups = (ngroups_total - r + p.NP - 1) / p.NP;  // groups r, r+NP, ...
-  const WaitCtx w{abort_flag, p.status};
+  const WaitCtx w{smem_u32(abort_flag), p.status};
 
 #ifdef FTA_TRACE
   if (threadIdx.x < 256) s_trace[threadIdx.x] = 0;

@@ -108,8 +108,9 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   using C = FwdCfg<kD>;
   constexpr int G = C::G;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+  // 1 KB alignment by an offset from the shared array itself, so that the compiler keeps the
+  // shared address space (ld.shared / st.shared instead of generic accesses)
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sQ = smem + C::OFF_Q;
   uint8_t* sKV = smem + C::OFF_KV;
   uint8_t* sBias = smem + C::OFF_BIAS;
@@ -131,7 +132,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   auto unit_i0 = [&](int u) { return (static_cast<int>(blockIdx.y) + u * static_cast<int>(gridDim.y)) * G; };
   // rows processed in a unit (an odd tail is padded with a zero row)
   auto unit_gp = [&](int u) { return (min(G, p.L1 - unit_i0(u)) + 1) & ~1; };
-  const WaitCtx w{abort_flag, p.status};
+  const WaitCtx w{smem_u32(abort_flag), p.status};
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;

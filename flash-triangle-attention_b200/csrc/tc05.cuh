@@ -91,9 +91,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t pa
 
 // Shared abort flag + global status word, carried by every role.
 struct WaitCtx {
-  volatile int* abort_flag;  // shared memory, one per CTA
+  uint32_t abort_addr;  // shared-memory address of the CTA's abort word
   int* status;               // global memory, one per launch
 };
+
+__device__ __forceinline__ uint32_t ld_shared_volatile_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_volatile_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -111,14 +120,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   unsigned long long t0 = 0;
   for (uint32_t it = 0; it < (1u << 30); ++it) {
     if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
-    if (*w.abort_flag) return false;
+    if (ld_shared_volatile_u32(w.abort_addr)) return false;
     if ((it & 0x3ff) == 0x3ff) {
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > 1000000000ull) break;
     }
   }
-  *w.abort_flag = 1;
+  st_shared_volatile_u32(w.abort_addr, 1u);
   atomicCAS(w.status, kStatusOk, kStatusWaitTimeout | site);
   return false;
 }
