@@ -189,6 +189,14 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
   if ((rc = map5(&a.tmQ, prob, q)) || (rc = map5(&a.tmK, prob, k)) || (rc = map5(&a.tmV, prob, v)) ||
       (rc = map5(&a.tmDO, prob, dout)) || (rc = map_bias(&a.tmBiasT, prob, &bt, 64, 128)))
     return rc;
+  {
+    // dq32 seen as (rows, D) float32; the kernel adds 128-row x 32-column tiles into it with TMA reductions
+    if (rows >= (1ull << 31)) return FTA_ERR_SHAPE;  // tile coordinates are signed 32-bit
+    const uint64_t dims[2] = {static_cast<uint64_t>(prob->D), rows};
+    const uint64_t str[2] = {0, static_cast<uint64_t>(prob->D) * 4};
+    const uint32_t box[2] = {32, 128};
+    if (fta::make_tmap(&a.tmDQ, 4, dq32, 2, dims, str, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
+  }
   a.lse = lse;
   a.delta = delta;
   a.dq32 = dq32;

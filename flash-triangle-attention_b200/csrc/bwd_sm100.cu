@@ -25,7 +25,7 @@
 // dQ leaves the CTA as float32 reductions into a zero-initialised buffer (sum over key blocks).
 //
 //   warp 0     : tcgen05 issuer (lowest warp id: the scheduler prefers older warps)
-//   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : idle
+//   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : dQ store warp (TMA reductions)
 //   warps 4-19 : four compute warpgroups, one 32-query quarter of the tile each; quarters 0-1
 //                (half 0) also store dV, quarters 2-3 (half 1) store dK; each reduces a quarter of dQ
 // Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
@@ -61,7 +61,11 @@ __device__ unsigned long long g_trace_bwd[8192];
 template <int kD>
 struct BwdCfg {
   static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + 2*D + 2*D*G <= 512)
-  static constexpr int NQ = (kD == 32) ? 4 : 2;  // Q/dO ring depth
+  static constexpr int NQ = (kD == 32) ? 3 : 2;  // Q/dO ring depth
+  // dQ tiles leave through a shared-memory staging tile and a TMA reduction (D = 32); at D = 64
+  // shared memory has no room for the tile and dQ is reduced with red.global from registers
+  static constexpr bool DQ_TMA = (kD == 32);
+  static constexpr int DQS_B = DQ_TMA ? 128 * 32 * 4 : 0;
   static constexpr int TILE_B = 128 * kD * 2;
   static constexpr int STAGE_B = 2 * TILE_B + 2048;  // Q, dO, -max[128], -log2sum[128], delta[128], c[128]
   static constexpr int BIAS_B = 128 * 128 * 2;
@@ -70,7 +74,8 @@ struct BwdCfg {
   static constexpr int OFF_QDO = OFF_KV + G * 2 * TILE_B;
   static constexpr int OFF_BIAS = OFF_QDO + NQ * STAGE_B;
   static constexpr int OFF_DS = OFF_BIAS + 2 * BIAS_B;
-  static constexpr int OFF_BAR = OFF_DS + DS_B;
+  static constexpr int OFF_DQS = OFF_DS + DS_B;
+  static constexpr int OFF_BAR = OFF_DQS + DQS_B;
   static constexpr int B_KVFULL = 0;
   static constexpr int B_KVFREE = 1;
   static constexpr int B_QDOFULL = 2;
@@ -84,7 +89,9 @@ struct BwdCfg {
   static constexpr int B_DQDONE = B_P2FULL + 2;
   static constexpr int B_ACCFULL = B_DQDONE + 1;
   static constexpr int B_ACCFREE = B_ACCFULL + 1;
-  static constexpr int NBAR = B_ACCFREE + 1;
+  static constexpr int B_DQSFULL = B_ACCFREE + 1;
+  static constexpr int B_DQSFREE = B_DQSFULL + 1;
+  static constexpr int NBAR = B_DQSFREE + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024 + 2048 + 16;  // + trace slots (debug builds)
   static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
   static constexpr uint32_t ROW_B = kD * 2;
@@ -130,7 +137,8 @@ template <int kD, bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
-               const __grid_constant__ CUtensorMap tmBiasT, const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmBiasT, const __grid_constant__ CUtensorMap tmDQ,
+               const BwdParams p) {
   using C = BwdCfg<kD>;
   constexpr int G = C::G;
   extern __shared__ uint8_t smem_raw[];
@@ -141,6 +149,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint8_t* sQDO = smem + C::OFF_QDO;  // [stage][Q | dO | lse | delta]
   uint8_t* sBias = smem + C::OFF_BIAS;  // [stage][query half][key row][64 queries], 128B swizzle
   uint8_t* sDS = smem + C::OFF_DS;
+  uint8_t* sDQ = smem + C::OFF_DQS;  // float32 dQ tile on its way to the TMA reduction
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
@@ -182,6 +191,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(bar(C::B_DQDONE), 1);
     mbar_init(bar(C::B_ACCFULL), 1);
     mbar_init(bar(C::B_ACCFREE), 16);
+    mbar_init(bar(C::B_DQSFULL), 16);
+    mbar_init(bar(C::B_DQSFREE), 1);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -203,6 +214,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_prefetch_desc(&tmV);
         tma_prefetch_desc(&tmDO);
         tma_prefetch_desc(&tmBiasT);
+        tma_prefetch_desc(&tmDQ);
       }
       bool ok = true;
       int tt = 0, nb = 0;
@@ -217,6 +229,14 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL), 0, kb * 128, i0 + g, h, b);
             tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL), 0, kb * 128,
                         i0 + g, h, b);
+          }
+          // K/V of the next group are read by no other CTA: bring them into L2 a whole group ahead
+          if (n + 1 < ngroups) {
+            const int i1 = (r + (n + 1) * p.NP) * G;
+            for (int g = 0; g < min(G, p.L1 - i1); ++g) {
+              tma_prefetch_l2_5d(&tmK, 0, kb * 128, i1 + g, h, b);
+              tma_prefetch_l2_5d(&tmV, 0, kb * 128, i1 + g, h, b);
+            }
           }
         }
         for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
@@ -306,7 +326,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int jb = t / Gc, g = t % Gc, gn = (t + 1) % Gc;
           const bool more = t + 1 < T;
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 1 done: dV, then the next S^T
+            if (wh == 0 && lane == 0) FTA_SSTAMP(0, tt);
             ok = mbar_wait_warp(bar(C::B_P1FULL + wh), tt & 1, w, 0x33);
+            if (lane == 0) FTA_SSTAMP(1 + wh, tt);
             if (ok && t == 0 && wh == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
             if (ok && more && wh == 0)
               ok = mbar_wait_warp(bar(C::B_QDOFULL + (tt + 1) % C::NQ), ((tt + 1) / C::NQ) & 1, w, 0x35);
@@ -316,7 +338,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (more) issue_half(0, tt + 1, gn, wh);
           }
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 2 done: dK, then the next dP^T
+            if (wh == 0 && lane == 0) FTA_SSTAMP(3, tt);
             ok = mbar_wait_warp(bar(C::B_P2FULL + wh), tt & 1, w, 0x39);
+            if (lane == 0) FTA_SSTAMP(4 + wh, tt);
             if (!ok) break;
             tc_fence_after_sync();
             issue_acc(1, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
@@ -325,6 +349,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               __syncwarp();
             }
             if (more) issue_half(1, tt + 1, gn, wh);
+            if (wh == 1 && lane == 0) FTA_SSTAMP(6, tt);
           }
         }
         if (ok) {
@@ -370,6 +395,30 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           __syncwarp();
         }
       }
+    } else if (C::DQ_TMA) {
+      // ---------------------------------------------------------------- store warp
+      // Adds each finished dQ tile (float32, staged in shared memory by the compute warps) into
+      // the dQ accumulator with one TMA reduction: whole 128-byte rows, issued by one thread.
+      bool ok = true;
+      int k = 0;  // dQ tiles so far
+      for (int n = 0; n < ngroups && ok; ++n) {
+        const int i0 = (r + n * p.NP) * G;
+        const int Gc = min(G, p.L1 - i0);
+        for (int t = 0; t < nq * Gc && ok; ++t, ++k) {
+          ok = mbar_wait_warp(bar(C::B_DQSFULL), k & 1, w, 0x51);
+          if (!ok) break;
+          if (elect_one()) {
+            const long long row0 = (static_cast<long long>(bh) * p.L1 + i0 + t % Gc) * p.L2 + (t / Gc) * 128;
+            tma_reduce_add_2d(&tmDQ, smem_u32(sDQ), 0, static_cast<int>(row0));
+            bulk_commit_group();
+            bulk_wait_read_all();  // the staging tile has been read: the compute warps may refill it
+            mbar_arrive(bar(C::B_DQSFREE));
+          }
+          __syncwarp();
+        }
+      }
+      if (elect_one()) bulk_wait_all();
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
@@ -393,8 +442,27 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     int tt = 0, nb = 0;
     // reduce this warpgroup's quarter of the columns of one finished dQ tile (TMEM buffer `buf`)
     // into the float32 dQ accumulator; the four warpgroups share the work evenly
-    auto reduce_dq = [&](int buf, int irow, int jblk) {
+    int kdq = 0;  // dQ tiles handed to the store warp so far
+    auto reduce_dq = [&](int buf, int irow, int jblk) -> bool {
       constexpr int W = kD / 4;  // columns per warpgroup
+      if constexpr (C::DQ_TMA) {
+        // this warpgroup's 8 columns (two 16-byte chunks) of each row of the staging tile, in the
+        // 128-byte swizzle the tensor map expects; the tile is free once the store warp says that
+        // the previous reduction has read it
+        uint32_t qv[8];
+        tmem_ld8(tbase + C::TM_DQ + buf * kD + qd * W + lane_off, qv);
+        const bool free_ok = kdq == 0 || mbar_wait_warp(bar(C::B_DQSFREE), (kdq - 1) & 1, w, 0x48);
+        tmem_ld_wait();
+        if (!free_ok) return false;
+        const uint32_t rowa = smem_u32(sDQ) + key * 128;
+        st_shared_v4(rowa + (((2 * qd) ^ (key & 7)) << 4), qv[0], qv[1], qv[2], qv[3]);
+        st_shared_v4(rowa + (((2 * qd + 1) ^ (key & 7)) << 4), qv[4], qv[5], qv[6], qv[7]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::B_DQSFULL));
+        ++kdq;
+        return true;
+      }
       float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128 + key) * kD + qd * W;
 #pragma unroll
       for (int c = 0; c < W / 8; ++c) {
@@ -406,6 +474,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         red_add_v4(dst + c * 8 + 4, __uint_as_float(qv[4]), __uint_as_float(qv[5]), __uint_as_float(qv[6]),
                    __uint_as_float(qv[7]));
       }
+      return true;
     };
     for (int n = 0; n < ngroups && ok; ++n) {
       const int i0 = (r + n * p.NP) * G;
@@ -421,12 +490,12 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int g = 0; g < Gc; ++g, ++tt) {
           const int s = tt % C::NQ;
           const uint8_t* st = sQDO + s * C::STAGE_B;
-          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 0, tt);
+          if ((warp & 3) == 0) FTA_STAMP(qd, 0, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // statistics visible
           if (!ok) break;
-          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 1, tt);
+          if ((warp & 3) == 0) FTA_STAMP(qd, 1, tt);
           tc_fence_after_sync();
           const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + qd * 8;
           const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + qd * 8;
@@ -504,11 +573,12 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
-          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 2, tt);
+          if ((warp & 3) == 0) FTA_STAMP(qd, 2, tt);
           // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
           ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
           if (!ok) break;
           tc_fence_after_sync();
+          if ((warp & 3) == 0) FTA_STAMP(qd, 3, tt);
           uint32_t dd[16];  // dS^T of this key row, 32 queries, packed 16-bit pairs
 #pragma unroll
           for (int c16 = 0; c16 < 2; ++c16) {
@@ -534,10 +604,12 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
           }
           tmem_st16(tDP, dd);
+          if ((warp & 3) == 0) FTA_STAMP(qd, 4, tt);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
             if (!ok) break;
           }
+          if ((warp & 3) == 0) FTA_STAMP(qd, 5, tt);
           // dS^T row of this key into the M-major staging tile (128-byte swizzle)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -549,14 +621,15 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_P2FULL + wh));
-          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 3, tt);
+          if ((warp & 3) == 0) FTA_STAMP(qd, 6, tt);
           if (!(jb == 0 && g == 0)) {
             // dQ of the previous tile of this group is complete (DQDONE waited above)
             const int pt = jb * Gc + g - 1;
             tc_fence_after_sync();
-            reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+            ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+            if (!ok) break;
           }
-          if ((warp & 3) == 0 && sub == 0) FTA_STAMP(wh, 4, tt);
+          if ((warp & 3) == 0) FTA_STAMP(qd, 7, tt);
         }
         if (!ok) break;
         // bias stage no longer needed by this warp
@@ -592,7 +665,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (!ok) break;
         tc_fence_after_sync();
         const int pt = nq * Gc - 1;
-        reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+        ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+        if (!ok) break;
       }
       {
         // half 0 stores dV, half 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518); the two
@@ -634,7 +708,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   if (warp == 0) tmem_dealloc(tbase, 512);
 #ifdef FTA_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0)
-    for (int i = 0; i < 256; ++i) g_trace_bwd[3 * 512 + i] = s_trace[i];
+    for (int i = 0; i < 256; ++i) g_trace_bwd[5 * 512 + i] = s_trace[i];
 #endif
 }
 
@@ -668,7 +742,7 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   p.scale = a.sm_scale;
   p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
   const int grid = a.B * a.H * NP * (a.L2 / 128);
-  kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, p);
+  kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, a.tmDQ, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -22,7 +22,8 @@ int fwd_rows_per_cta(int D);
 
 struct BwdArgs {
   CUtensorMap tmQ, tmK, tmV, tmDO, tmBiasT;  // tmBiasT: over the key-major copy of the bias
-  const float* lse;    // (2,B,H,L1,L2): -max, -log2(sum)
+  CUtensorMap tmDQ;    // dq32 as a 2-D float32 tensor (rows, D), box 128 rows x 32 columns, 128 B swizzle
+  const float* lse;    // (3,B,H,L1,L2): -max, -log2(sum), combined (NaN where inexact)
   const float* delta;  // (B,H,L1,L2)
   float* dq32;         // (B,H,L1,L2,D) float32, zeroed; receives sum over key blocks of dS K
   void* dk;

@@ -25,15 +25,16 @@ inline EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// Build a tiled map over a tensor of 16-bit elements.
+// Build a tiled map.
+//   elem_bytes : 2 (16-bit elements, fp16 or bf16 alike) or 4 (float32)
 //   rank     : 2..5
 //   dims[r]  : extent of dimension r, innermost first
 //   strides[r] : BYTE stride of dimension r for r >= 1 (dimension 0 is dense)
 //   box[r]   : tile extent of dimension r
 //   swizzle_bytes : 0, 32, 64 or 128
 // Returns 0 on success, the CUresult (or -1 if the entry point is missing) otherwise.
-inline int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                           const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+inline int make_tmap(CUtensorMap* out, int elem_bytes, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return -1;
   cuuint64_t gdim[5];
@@ -50,10 +51,16 @@ inline int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const u
   if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
   else if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
   else if (swizzle_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, static_cast<cuuint32_t>(rank),
-                   const_cast<void*>(base), gdim, gstr, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
+  CUresult r = enc(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, gbox, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return static_cast<int>(r);
+}
+
+inline int make_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box, int swizzle_bytes) {
+  return make_tmap(out, 2, base, rank, dims, strides_bytes, box, swizzle_bytes);
 }
 
 }  // namespace fta
