@@ -196,13 +196,18 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
     const uint64_t str[2] = {0, static_cast<uint64_t>(prob->D) * 4};
     const uint32_t box[2] = {32, 128};
     if (fta::make_tmap(&a.tmDQ, 4, dq32, 2, dims, str, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
+    // the partial dBias planes, key-major: (nplanes * B*H * L2 key rows, L2 queries) float32
+    const uint64_t prow = static_cast<uint64_t>(nplanes) * prob->B * prob->H * prob->L2;
+    if (prow >= (1ull << 31)) return FTA_ERR_SHAPE;
+    const uint64_t pdims[2] = {static_cast<uint64_t>(prob->L2), prow};
+    const uint64_t pstr[2] = {0, static_cast<uint64_t>(prob->L2) * 4};
+    if (fta::make_tmap(&a.tmPlane, 4, planes, 2, pdims, pstr, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
   }
   a.lse = lse;
   a.delta = delta;
   a.dq32 = dq32;
   a.dk = dk->ptr;
   a.dv = dv->ptr;
-  a.planes = planes;
   a.status = status;
   a.B = prob->B;
   a.H = prob->H;
@@ -230,7 +235,8 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
   if (fta::launch_dq_finalize(dq32, dq->ptr, sdq, prob->B, prob->H, prob->L1, prob->L2, prob->D, sm_scale, bf16,
                               st) != 0)
     return cuda_fail(cudaGetLastError());
-  if (fta::launch_dbias_finalize(planes, nplanes, plane_elems, dbias_f32, dbias_cast, bf16, st) != 0)
+  if (fta::launch_dbias_finalize_keymajor(planes, nplanes, prob->B * prob->H, prob->L2, dbias_f32, dbias_cast, bf16,
+                                          st) != 0)
     return cuda_fail(cudaGetLastError());
   return FTA_OK;
 }

@@ -43,6 +43,8 @@ constexpr int kComputeRegs = 104;   // 512 * 104 + 128 * 56 <= 640 * 96, the CTA
 #ifdef FTA_TRACE
 // Debug build only: clock64() stamps of CTA 0, read back with fta_trace_read_bwd().
 __device__ unsigned long long g_trace_bwd[8192];
+#endif
+#if defined(FTA_TRACE) && !defined(FTA_NOSTAMP)
 #define FTA_STAMP(role, ev, tile)                                                  \
   do {                                                                             \
     if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile) < 64)                 \
@@ -56,6 +58,35 @@ __device__ unsigned long long g_trace_bwd[8192];
 #else
 #define FTA_STAMP(role, ev, tile) do { } while (0)
 #define FTA_SSTAMP(ev, tile) do { } while (0)
+#endif
+
+#ifdef FTA_PROGRESS
+// Debug build only: each warp notes where it is (code, counter) in shared memory; a CTA that
+// aborts copies the notes and the parity of every barrier to global memory at tear-down.
+__device__ unsigned long long g_progress[128];
+#define FTA_PROG(code, cnt)                                                                  \
+  do {                                                                                       \
+    if ((threadIdx.x & 31) == 0) s_prog[threadIdx.x >> 5] = ((unsigned)(code) << 20) | ((unsigned)(cnt) & 0xfffff); \
+  } while (0)
+#else
+#define FTA_PROG(code, cnt) do { } while (0)
+#endif
+
+// experiment switches (timing studies only; the defaults are the real kernel)
+#ifndef FTA_EXP_P1
+#define FTA_EXP_P1 2
+#endif
+#ifndef FTA_EXP_P2
+#define FTA_EXP_P2 2
+#endif
+#ifndef FTA_EXP_DUMP
+#define FTA_EXP_DUMP 4
+#endif
+#ifndef FTA_EXP_DQ_OUT
+#define FTA_EXP_DQ_OUT true
+#endif
+#ifndef FTA_EXP_PLANE_OUT
+#define FTA_EXP_PLANE_OUT true
 #endif
 
 template <int kD>
@@ -91,7 +122,13 @@ struct BwdCfg {
   static constexpr int B_ACCFREE = B_ACCFULL + 1;
   static constexpr int B_DQSFULL = B_ACCFREE + 1;
   static constexpr int B_DQSFREE = B_DQSFULL + 1;
-  static constexpr int NBAR = B_DQSFREE + 1;
+  // dBias flush of query half h: box of its first / second warpgroup written, first box read.
+  // One barrier per turn: a single one would see two phases per query block, and the store warp
+  // may lag a whole phase behind, which a parity wait cannot tell from being on time.
+  static constexpr int B_FLA = B_DQSFREE + 1;
+  static constexpr int B_FLB = B_FLA + 2;
+  static constexpr int B_DSFREE = B_FLB + 2;  // the two boxes parked in the dS tile have been read
+  static constexpr int NBAR = B_DSFREE + 1;
   static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024 + 2048 + 16;  // + trace slots (debug builds)
   static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
   static constexpr uint32_t ROW_B = kD * 2;
@@ -110,7 +147,6 @@ struct BwdParams {
   float* dq32;
   void* dk;
   void* dv;
-  float* planes;
   int* status;
   int H, L1, L2, NP, BH;
   long long sdk[4], sdv[4];
@@ -129,16 +165,13 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
-__device__ __forceinline__ void red_add(float* addr, float a) {
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(a) : "memory");
-}
 
 template <int kD, bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                const __grid_constant__ CUtensorMap tmBiasT, const __grid_constant__ CUtensorMap tmDQ,
-               const BwdParams p) {
+               const __grid_constant__ CUtensorMap tmPlane, const BwdParams p) {
   using C = BwdCfg<kD>;
   constexpr int G = C::G;
   extern __shared__ uint8_t smem_raw[];
@@ -156,6 +189,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #ifdef FTA_TRACE
   unsigned long long* s_trace = reinterpret_cast<unsigned long long*>(abort_flag + 3);
 #endif
+#ifdef FTA_PROGRESS
+  volatile unsigned* s_prog = reinterpret_cast<volatile unsigned*>(abort_flag + 4);
+#endif
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
@@ -167,7 +203,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int b = bh / p.H, h = bh % p.H;
   const int ngroups_total = (p.L1 + G - 1) / G;
   const int ngroups = (ngroups_total - r + p.NP - 1) / p.NP;  // groups r, r+NP, ...
+#ifdef FTA_TRACE
+  const WaitCtx w{smem_u32(abort_flag), p.status, blockIdx.x == 0 ? g_trace_bwd + 15 * 512 : nullptr};
+#else
   const WaitCtx w{smem_u32(abort_flag), p.status};
+#endif
 
 #ifdef FTA_TRACE
   if (threadIdx.x < 256) s_trace[threadIdx.x] = 0;
@@ -182,7 +222,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::B_BIASFULL + i), 1);
-      mbar_init(bar(C::B_BIASEMPTY + i), 16);  // one arrive per compute warp
+      mbar_init(bar(C::B_BIASEMPTY + i), 1);   // store warp, once the boxes parked in the stage are read
+      mbar_init(bar(C::B_FLA + i), 4);         // the four warps of the warpgroup that wrote the box
+      mbar_init(bar(C::B_FLB + i), 4);
       mbar_init(bar(C::B_SFULL + i), 1);
       mbar_init(bar(C::B_DPFULL + i), 1);
       mbar_init(bar(C::B_P1FULL + i), 8);  // one arrive per warp of the two warpgroups of a half
@@ -193,6 +235,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     mbar_init(bar(C::B_ACCFREE), 16);
     mbar_init(bar(C::B_DQSFULL), 16);
     mbar_init(bar(C::B_DQSFREE), 1);
+    mbar_init(bar(C::B_DSFREE), 1);
     mbar_fence_init();
   }
   if (warp == 0) {
@@ -215,12 +258,14 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_prefetch_desc(&tmDO);
         tma_prefetch_desc(&tmBiasT);
         tma_prefetch_desc(&tmDQ);
+        tma_prefetch_desc(&tmPlane);
       }
       bool ok = true;
       int tt = 0, nb = 0;
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = (r + n * p.NP) * G;
         const int Gc = min(G, p.L1 - i0);
+        FTA_PROG(0x12, n);
         ok = mbar_wait_warp(bar(C::B_KVFREE), (n & 1) ^ 1, w, 0x21);
         if (!ok) break;
         if (elect_one()) {
@@ -241,6 +286,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
           const int bs = nb & 1;
+          FTA_PROG(0x10, nb);
           ok = mbar_wait_warp(bar(C::B_BIASEMPTY + bs), ((nb >> 1) & 1) ^ 1, w, 0x22);
           if (!ok) break;
           if (elect_one()) {
@@ -253,6 +299,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           for (int g = 0; g < Gc; ++g, ++tt) {
             const int s = tt % C::NQ;
+            FTA_PROG(0x11, tt);
             ok = mbar_wait_warp(bar(C::B_QDOEMPTY + s), ((tt / C::NQ) & 1) ^ 1, w, 0x23);
             if (!ok) break;
             if (elect_one()) {
@@ -314,6 +361,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int i0 = (r + n * p.NP) * G;
         const int Gc = min(G, p.L1 - i0);
         const int T = nq * Gc;
+        FTA_PROG(0x25, n);
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32) &&
              mbar_wait_warp(bar(C::B_QDOFULL + tt % C::NQ), (tt / C::NQ) & 1, w, 0x31);
         if (!ok) break;
@@ -327,11 +375,14 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const bool more = t + 1 < T;
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 1 done: dV, then the next S^T
             if (wh == 0 && lane == 0) FTA_SSTAMP(0, tt);
+            FTA_PROG(0x20 + wh, tt);
             ok = mbar_wait_warp(bar(C::B_P1FULL + wh), tt & 1, w, 0x33);
             if (lane == 0) FTA_SSTAMP(1 + wh, tt);
             if (ok && t == 0 && wh == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
-            if (ok && more && wh == 0)
+            if (ok && more && wh == 0) {
+              FTA_PROG(0x24, tt);
               ok = mbar_wait_warp(bar(C::B_QDOFULL + (tt + 1) % C::NQ), ((tt + 1) / C::NQ) & 1, w, 0x35);
+            }
             if (!ok) break;
             tc_fence_after_sync();
             issue_acc(0, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
@@ -339,6 +390,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 2 done: dK, then the next dP^T
             if (wh == 0 && lane == 0) FTA_SSTAMP(3, tt);
+            FTA_PROG(0x22 + wh, tt);
             ok = mbar_wait_warp(bar(C::B_P2FULL + wh), tt & 1, w, 0x39);
             if (lane == 0) FTA_SSTAMP(4 + wh, tt);
             if (!ok) break;
@@ -375,6 +427,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x36);
         for (int t = 0; t < T && ok; ++t, ++tt) {
           const int g = t % Gc;
+          FTA_PROG(0x30, tt);
           ok = mbar_wait_warp(bar(C::B_P2FULL + 0), tt & 1, w, 0x37) &&
                mbar_wait_warp(bar(C::B_P2FULL + 1), tt & 1, w, 0x38);
           if (!ok) break;
@@ -395,28 +448,91 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           __syncwarp();
         }
       }
-    } else if (C::DQ_TMA) {
+    } else {
       // ---------------------------------------------------------------- store warp
-      // Adds each finished dQ tile (float32, staged in shared memory by the compute warps) into
-      // the dQ accumulator with one TMA reduction: whole 128-byte rows, issued by one thread.
+      // Everything that leaves the CTA as a float32 sum goes through shared memory and one TMA
+      // tile reduction issued by one thread (whole 128-byte lines, no work for the compute warps):
+      //  * each finished dQ tile, staged by the compute warps (D = 32);
+      //  * at the end of each query block, the dBias sums of the four warpgroups: 16 KB boxes
+      //    (128 keys x 32 queries) written into the bias stage that has just been used up - the two
+      //    warpgroups of a query half take turns in that half's 16 KB - and added to (first group:
+      //    stored into) this CTA's private key-major plane.
       bool ok = true;
-      int k = 0;  // dQ tiles so far
+      int k = 0, nb = 0;  // dQ tiles / query blocks so far
+      auto dq_event = [&](int irow, int jblk) -> bool {
+        FTA_PROG(0x40, k);
+        if (!mbar_wait_warp(bar(C::B_DQSFULL), k & 1, w, 0x51)) return false;
+        if (elect_one()) {
+          const long long row0 = (static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128;
+          if (FTA_EXP_DQ_OUT) tma_reduce_add_2d(&tmDQ, smem_u32(sDQ), 0, static_cast<int>(row0));
+          bulk_commit_group();
+          bulk_wait_read_all();  // the staging tile has been read: the compute warps may refill it
+          mbar_arrive(bar(C::B_DQSFREE));
+        }
+        __syncwarp();
+        ++k;
+        return true;
+      };
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = (r + n * p.NP) * G;
         const int Gc = min(G, p.L1 - i0);
-        for (int t = 0; t < nq * Gc && ok; ++t, ++k) {
-          ok = mbar_wait_warp(bar(C::B_DQSFULL), k & 1, w, 0x51);
+        const int prow = (r * p.BH + bh) * p.L2 + kb * 128;  // first key row of this CTA's plane tile
+        for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
+          if constexpr (C::DQ_TMA) {
+            for (int g = 0; g < Gc && ok; ++g) {
+              if (jb == 0 && g == 0) continue;
+              const int pt = jb * Gc + g - 1;
+              ok = dq_event(i0 + pt % Gc, pt / Gc);
+            }
+            if (!ok) break;
+          }
+          const int bs = nb & 1;
+          // second warpgroup of each half: boxes parked in the dS tile (needed again soonest)
+          FTA_PROG(0x41, nb);
+          ok = mbar_wait_warp(bar(C::B_FLB + 0), nb & 1, w, 0x52) && mbar_wait_warp(bar(C::B_FLB + 1), nb & 1, w, 0x53);
           if (!ok) break;
           if (elect_one()) {
-            const long long row0 = (static_cast<long long>(bh) * p.L1 + i0 + t % Gc) * p.L2 + (t / Gc) * 128;
-            tma_reduce_add_2d(&tmDQ, smem_u32(sDQ), 0, static_cast<int>(row0));
+            for (int hh = 0; hh < 2; ++hh) {
+              const uint32_t src = smem_u32(sDS + hh * 16384);
+              const int qcol = jb * 128 + (2 * hh + 1) * 32;
+              if (!(FTA_EXP_PLANE_OUT)) continue;
+              if (n == 0) tma_store_2d(&tmPlane, src, qcol, prow);
+              else tma_reduce_add_2d(&tmPlane, src, qcol, prow);
+            }
             bulk_commit_group();
-            bulk_wait_read_all();  // the staging tile has been read: the compute warps may refill it
-            mbar_arrive(bar(C::B_DQSFREE));
+          }
+          __syncwarp();
+          // first warpgroup of each half: boxes parked in the bias stage
+          FTA_PROG(0x42, nb);
+          ok = mbar_wait_warp(bar(C::B_FLA + 0), nb & 1, w, 0x54) && mbar_wait_warp(bar(C::B_FLA + 1), nb & 1, w, 0x55);
+          if (!ok) break;
+          if (elect_one()) {
+            for (int hh = 0; hh < 2; ++hh) {
+              const uint32_t src = smem_u32(sBias + bs * C::BIAS_B + hh * 16384);
+              const int qcol = jb * 128 + (2 * hh) * 32;
+              if (!(FTA_EXP_PLANE_OUT)) continue;
+              if (n == 0) tma_store_2d(&tmPlane, src, qcol, prow);
+              else tma_reduce_add_2d(&tmPlane, src, qcol, prow);
+            }
+            bulk_commit_group();
+            bulk_wait_read_le1();  // the older group (dS tile) has been read
+            mbar_arrive(bar(C::B_DSFREE));
+            bulk_wait_read_all();
+            mbar_arrive(bar(C::B_BIASEMPTY + bs));  // the bias stage goes back to the producer
           }
           __syncwarp();
         }
+        if (!ok) break;
+        if constexpr (C::DQ_TMA) {
+          const int pt = nq * Gc - 1;
+          ok = dq_event(i0 + pt % Gc, pt / Gc);
+        }
+        // the next group adds to the plane elements this group wrote: finish these writes first
+        FTA_PROG(0x45, n);
+        if (elect_one()) bulk_wait_all();
+        __syncwarp();
       }
+      FTA_PROG(0x46, 0);
       if (elect_one()) bulk_wait_all();
       __syncwarp();
     }
@@ -433,7 +549,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // this quarter's 32 fp32 columns of S^T / dP^T; P^T / dS^T overwrite its first 16 columns
     const uint32_t tST = tbase + C::TM_ST + wh * 64 + sub * 32 + lane_off;
     const uint32_t tDP = tbase + C::TM_DP + wh * 64 + sub * 32 + lane_off;
-    float* plane = p.planes + (static_cast<long long>(r) * p.BH + bh) * p.L2 * p.L2;
     const f32x2 scale2 = mk2(p.scale, p.scale);
     const f32x2 log2e2 = mk2(kLog2e, kLog2e);
     const f32x2 k1_2 = mk2(p.scale * kLog2e, p.scale * kLog2e);
@@ -443,7 +558,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // reduce this warpgroup's quarter of the columns of one finished dQ tile (TMEM buffer `buf`)
     // into the float32 dQ accumulator; the four warpgroups share the work evenly
     int kdq = 0;  // dQ tiles handed to the store warp so far
-    auto reduce_dq = [&](int buf, int irow, int jblk) -> bool {
+    // `publish`: fence and tell the store warp here; otherwise the caller does both (it shares
+    // the fence with its own shared-memory writes)
+    auto reduce_dq = [&](int buf, int irow, int jblk, bool publish) -> bool {
       constexpr int W = kD / 4;  // columns per warpgroup
       if constexpr (C::DQ_TMA) {
         // this warpgroup's 8 columns (two 16-byte chunks) of each row of the staging tile, in the
@@ -457,10 +574,12 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t rowa = smem_u32(sDQ) + key * 128;
         st_shared_v4(rowa + (((2 * qd) ^ (key & 7)) << 4), qv[0], qv[1], qv[2], qv[3]);
         st_shared_v4(rowa + (((2 * qd + 1) ^ (key & 7)) << 4), qv[4], qv[5], qv[6], qv[7]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(C::B_DQSFULL));
         ++kdq;
+        if (publish) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::B_DQSFULL));
+        }
         return true;
       }
       float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128 + key) * kD + qd * W;
@@ -484,13 +603,16 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < 16; ++c) acc[c] = mk2(0.f, 0.f);
         const int bs = nb & 1;
+        FTA_PROG(0x54, nb);
         ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
         if (!ok) break;
+        if ((warp & 3) == 0) FTA_STAMP(6 + qd, 0, nb);
         const uint8_t* brow = sBias + bs * C::BIAS_B + wh * 16384 + key * 128;
         for (int g = 0; g < Gc; ++g, ++tt) {
           const int s = tt % C::NQ;
           const uint8_t* st = sQDO + s * C::STAGE_B;
           if ((warp & 3) == 0) FTA_STAMP(qd, 0, tt);
+          FTA_PROG(0x50, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // statistics visible
@@ -511,7 +633,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!robust) {
             // y = s*scale*log2e + b*log2e + c
 #pragma unroll
-            for (int c16 = 0; c16 < 2; ++c16) {
+            for (int c16 = 0; c16 < FTA_EXP_P1; ++c16) {
               uint32_t sv[16];
               tmem_ld16(tST + c16 * 16, sv);
               tmem_ld_wait();
@@ -575,13 +697,14 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
           if ((warp & 3) == 0) FTA_STAMP(qd, 2, tt);
           // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
+          FTA_PROG(0x51, tt);
           ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
           if (!ok) break;
           tc_fence_after_sync();
           if ((warp & 3) == 0) FTA_STAMP(qd, 3, tt);
           uint32_t dd[16];  // dS^T of this key row, 32 queries, packed 16-bit pairs
 #pragma unroll
-          for (int c16 = 0; c16 < 2; ++c16) {
+          for (int c16 = 0; c16 < FTA_EXP_P2; ++c16) {
             uint32_t dv[16];
             tmem_ld16(tDP + c16 * 16, dv);
             tmem_ld_wait();
@@ -606,13 +729,27 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_st16(tDP, dd);
           if ((warp & 3) == 0) FTA_STAMP(qd, 4, tt);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
+            FTA_PROG(0x52, tt);
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
+            if (!ok) break;
+          }
+          if (g == 0 && nb > 0) {  // the dBias boxes parked in the dS tile have been read
+            ok = mbar_wait_warp(bar(C::B_DSFREE), (nb - 1) & 1, w, 0x4b);
+            if (!ok) break;
+          }
+          // dQ of the previous tile of this group is complete (DQDONE waited above): stage it now,
+          // so that one proxy fence covers it and the dS rows below
+          const bool stage_dq = C::DQ_TMA && !(jb == 0 && g == 0);
+          if (stage_dq) {
+            const int pt = jb * Gc + g - 1;
+            tc_fence_after_sync();
+            ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, false);
             if (!ok) break;
           }
           if ((warp & 3) == 0) FTA_STAMP(qd, 5, tt);
           // dS^T row of this key into the M-major staging tile (128-byte swizzle)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < FTA_EXP_DUMP; ++j) {
             const uint4 v4 = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
             *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + (((sub * 4 + j) ^ (key & 7)) << 4)) = v4;
           }
@@ -620,54 +757,65 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           fence_proxy_async_smem();
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(C::B_P2FULL + wh));
+          if (lane == 0) {
+            mbar_arrive(bar(C::B_P2FULL + wh));
+            if (stage_dq) mbar_arrive(bar(C::B_DQSFULL));
+          }
           if ((warp & 3) == 0) FTA_STAMP(qd, 6, tt);
-          if (!(jb == 0 && g == 0)) {
+          if (!C::DQ_TMA && !(jb == 0 && g == 0)) {
             // dQ of the previous tile of this group is complete (DQDONE waited above)
             const int pt = jb * Gc + g - 1;
             tc_fence_after_sync();
-            ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+            ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, true);
             if (!ok) break;
           }
           if ((warp & 3) == 0) FTA_STAMP(qd, 7, tt);
         }
         if (!ok) break;
-        // bias stage no longer needed by this warp
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
-        // dBias: add this CTA's sums over the G rows to its private plane
-        float* dst = plane + (static_cast<long long>(jb) * 128 + qd * 32) * p.L2 + kb * 128 + key;
-        if (n == 0) {
+        // ---- dBias of this query block: the sums go to the store warp as 16 KB boxes parked in
+        // shared memory that is idle at this point. The first warpgroup of a half uses that half's
+        // part of the bias stage just used up (free once both warpgroups of the half have arrived
+        // for the last tile's phase 2), the second one that half's part of the dS tile (free once
+        // the last dQ MMA has read it).
+        FTA_PROG(0x53, nb);
+        if (sub == 0) ok = mbar_wait_warp(bar(C::B_P2FULL + wh), (tt - 1) & 1, w, 0x49);
+        else ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x4a);
+        if (!ok) break;
+        {
+          // box: 128 key rows x 32 queries (128 bytes), 128-byte swizzle
+          const uint32_t rowa = smem_u32(sub == 0 ? sBias + bs * C::BIAS_B + wh * 16384 : sDS + wh * 16384) + key * 128;
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            float a0, a1;
-            un2(acc[c], a0, a1);
-            dst[static_cast<long long>(2 * c) * p.L2] = a0;
-            dst[static_cast<long long>(2 * c + 1) * p.L2] = a1;
+          for (int j = 0; j < 8; ++j) {
+            float a0, a1, a2, a3;
+            un2(acc[2 * j], a0, a1);
+            un2(acc[2 * j + 1], a2, a3);
+            st_shared_v4(rowa + ((j ^ (key & 7)) << 4), __float_as_uint(a0), __float_as_uint(a1),
+                         __float_as_uint(a2), __float_as_uint(a3));
           }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            float a0, a1;
-            un2(acc[c], a0, a1);
-            red_add(dst + static_cast<long long>(2 * c) * p.L2, a0);
-            red_add(dst + static_cast<long long>(2 * c + 1) * p.L2, a1);
-          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar((sub == 0 ? C::B_FLA : C::B_FLB) + wh));
         }
+        if ((warp & 3) == 0) FTA_STAMP(6 + qd, 1, nb);
       }
       if (!ok) break;
       // ---- group epilogue: last dQ tile, then dK / dV of the G rows
+      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 0, n);
+      FTA_PROG(0x55, n);
       ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
       if (!ok) break;
+      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 1, n);
       tc_fence_after_sync();
       {
+        FTA_PROG(0x56, tt);
         ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
         if (!ok) break;
         tc_fence_after_sync();
         const int pt = nq * Gc - 1;
-        ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc);
+        ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, true);
         if (!ok) break;
       }
+      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 2, n);
       {
         // half 0 stores dV, half 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518); the two
         // warpgroups of a half take alternate rows of the group
@@ -698,6 +846,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::B_ACCFREE));
+      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 3, n);
     }
   }
 
@@ -705,6 +854,21 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) __nanosleep(20000);
+#ifdef FTA_PROGRESS
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && g_progress[127] == 0) atomicCAS(&g_progress[127], 0ull, (unsigned long long)blockIdx.x + 1);
+    __syncthreads();
+    if (g_progress[127] == blockIdx.x + 1) {
+      if (threadIdx.x < 20) g_progress[threadIdx.x] = s_prog[threadIdx.x];
+      if (threadIdx.x < C::NBAR) {
+        uint32_t p0;
+        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(p0) : "r"(bar(threadIdx.x)) : "memory");
+        g_progress[32 + threadIdx.x] = p0;  // 1: current phase index is odd
+      }
+    }
+  }
+#endif
   if (warp == 0) tmem_dealloc(tbase, 512);
 #ifdef FTA_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0)
@@ -728,7 +892,6 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   p.dq32 = a.dq32;
   p.dk = a.dk;
   p.dv = a.dv;
-  p.planes = a.planes;
   p.status = a.status;
   p.H = a.H;
   p.L1 = a.L1;
@@ -742,7 +905,7 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   p.scale = a.sm_scale;
   p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
   const int grid = a.B * a.H * NP * (a.L2 / 128);
-  kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, a.tmDQ, p);
+  kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, a.tmDQ, a.tmPlane, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -751,6 +914,12 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
 #ifdef FTA_TRACE
 int trace_read_bwd(unsigned long long* host, int n) {
   return cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
+}
+#endif
+
+#ifdef FTA_PROGRESS
+extern "C" __attribute__((visibility("default"))) int fta_progress_read(unsigned long long* host) {
+  return cudaMemcpyFromSymbol(host, g_progress, sizeof(unsigned long long) * 128) == cudaSuccess ? 0 : -1;
 }
 #endif
 

@@ -23,12 +23,12 @@ int fwd_rows_per_cta(int D);
 struct BwdArgs {
   CUtensorMap tmQ, tmK, tmV, tmDO, tmBiasT;  // tmBiasT: over the key-major copy of the bias
   CUtensorMap tmDQ;    // dq32 as a 2-D float32 tensor (rows, D), box 128 rows x 32 columns, 128 B swizzle
+  CUtensorMap tmPlane; // the partial dBias planes as (nplanes*B*H*L2 key rows, L2 queries) float32, same box
   const float* lse;    // (3,B,H,L1,L2): -max, -log2(sum), combined (NaN where inexact)
   const float* delta;  // (B,H,L1,L2)
   float* dq32;         // (B,H,L1,L2,D) float32, zeroed; receives sum over key blocks of dS K
   void* dk;
   void* dv;
-  float* planes;  // (nplanes, B*H, L2, L2) float32 partial dBias
   int* status;
   int B, H, L1, L2, D;
   bool bf16;
@@ -51,6 +51,11 @@ int launch_transpose_bias(const void* bias, const long long sb[4], void* out, in
 // out_f32[e] = sum_p planes[p][e] (fixed order), optional rounded copy
 int launch_dbias_finalize(const float* planes, int nplanes, long long plane_elems, float* out_f32,
                           void* out_cast, bool bf16, cudaStream_t stream);
+
+// The same for the KEY-MAJOR planes the backward kernel writes, (nplanes, B*H, key, query):
+// out[bh][query][key] = sum_p planes[p][bh][key][query] in plane order, optional rounded copy
+int launch_dbias_finalize_keymajor(const float* planes, int nplanes, int BH, int L2, float* out_f32,
+                                   void* out_cast, bool bf16, cudaStream_t stream);
 
 // dq[row, d] = (dtype)(scale * dq32[row, d])
 int launch_dq_finalize(const float* dq32, void* dq, const long long sdq[4], int B, int H, int L1,

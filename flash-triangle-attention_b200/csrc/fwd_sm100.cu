@@ -132,7 +132,11 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   auto unit_i0 = [&](int u) { return (static_cast<int>(blockIdx.y) + u * static_cast<int>(gridDim.y)) * G; };
   // rows processed in a unit (an odd tail is padded with a zero row)
   auto unit_gp = [&](int u) { return (min(G, p.L1 - unit_i0(u)) + 1) & ~1; };
+#ifdef FTA_TRACE
+  const WaitCtx w{smem_u32(abort_flag), p.status, nullptr};
+#else
   const WaitCtx w{smem_u32(abort_flag), p.status};
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;

@@ -92,6 +92,40 @@ __global__ void __launch_bounds__(256) dbias_finalize_kernel(const float* __rest
   }
 }
 
+// Key-major planes (p, bh, key, query) -> dBias (bh, query, key): 32 x 32 tiles transposed through
+// shared memory, the planes summed in index order on the way (bit-reproducible).
+template <bool kBf16>
+__global__ void __launch_bounds__(256) dbias_finalize_keymajor_kernel(const float* __restrict__ planes,
+                                                                      int nplanes, int BH, int L2,
+                                                                      float* __restrict__ out_f32,
+                                                                      uint16_t* __restrict__ out_cast) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int q0 = blockIdx.x * 32, k0 = blockIdx.y * 32, bh = blockIdx.z;
+  const long long plane_stride = static_cast<long long>(BH) * L2 * L2;
+  const float* src = planes + (static_cast<long long>(bh) * L2 + k0) * L2 + q0 + tx;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int pl = 0; pl < nplanes; ++pl) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      acc[i] += __ldg(src + static_cast<long long>(pl) * plane_stride + static_cast<long long>(ty + 8 * i) * L2);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) tile[ty + 8 * i][tx] = acc[i];  // [key][query]
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int q = ty + 8 * i;
+    const float v = tile[tx][q];
+    const long long o = (static_cast<long long>(bh) * L2 + q0 + q) * L2 + k0 + tx;
+    if (out_f32) out_f32[o] = v;
+    if (out_cast) {
+      const uint32_t pk = pack2<kBf16>(v, 0.f);
+      out_cast[o] = static_cast<uint16_t>(pk & 0xffffu);
+    }
+  }
+}
+
 template <int kD, bool kBf16>
 __global__ void __launch_bounds__(256) dq_finalize_kernel(const float* __restrict__ dq32,
                                                           uint16_t* __restrict__ dq, long long rows,
@@ -203,6 +237,18 @@ int launch_dbias_finalize(const float* planes, int nplanes, long long plane_elem
   else
     dbias_finalize_kernel<false><<<grid, 256, 0, stream>>>(planes, nplanes, plane_elems, out_f32,
                                                            static_cast<uint16_t*>(out_cast));
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int launch_dbias_finalize_keymajor(const float* planes, int nplanes, int BH, int L2, float* out_f32,
+                                   void* out_cast, bool bf16, cudaStream_t stream) {
+  const dim3 grid(L2 / 32, L2 / 32, BH);
+  if (bf16)
+    dbias_finalize_keymajor_kernel<true><<<grid, 256, 0, stream>>>(planes, nplanes, BH, L2, out_f32,
+                                                                   static_cast<uint16_t*>(out_cast));
+  else
+    dbias_finalize_keymajor_kernel<false><<<grid, 256, 0, stream>>>(planes, nplanes, BH, L2, out_f32,
+                                                                    static_cast<uint16_t*>(out_cast));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -93,7 +93,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t pa
 struct WaitCtx {
   uint32_t abort_addr;  // shared-memory address of the CTA's abort word
   int* status;               // global memory, one per launch
+#ifdef FTA_TRACE
+  unsigned long long* dbg;  // debug builds: where each warp of CTA 0 notes the wait it gave up at
+#endif
 };
+#if defined(FTA_TRACE)
+#define FTA_WAIT_NOTE(w, site, parity)                                                        \
+  do {                                                                                        \
+    if ((w).dbg && (threadIdx.x & 31) == 0) (w).dbg[threadIdx.x >> 5] = ((site) << 4) | (parity); \
+  } while (0)
+#else
+#define FTA_WAIT_NOTE(w, site, parity) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t ld_shared_volatile_u32(uint32_t addr) {
   uint32_t v;
@@ -117,16 +128,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   if (mbar_try_wait(bar, parity)) return true;
   // Spin on try_wait (which itself suspends the thread for a short, bounded time). The wait
   // gives up after about a second of wall-clock time, measured with the global nanosecond timer.
+  // The inner loop is nothing but the poll, so that a waiting warp takes as few issue slots as
+  // possible from the warps that share its scheduler; abort flag and clock are looked at once
+  // per 16 polls.
   unsigned long long t0 = 0;
-  for (uint32_t it = 0; it < (1u << 30); ++it) {
-    if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
-    if (ld_shared_volatile_u32(w.abort_addr)) return false;
-    if ((it & 0x3ff) == 0x3ff) {
+  for (uint32_t it = 0; it < (1u << 26); ++it) {
+#pragma unroll 1
+    for (int j = 0; j < 16; ++j)
+      if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (ld_shared_volatile_u32(w.abort_addr)) {
+      FTA_WAIT_NOTE(w, site, parity);
+      return false;
+    }
+    if ((it & 0x3f) == 0x3f) {
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > 1000000000ull) break;
     }
   }
+  FTA_WAIT_NOTE(w, site, parity);
   st_shared_volatile_u32(w.abort_addr, 1u);
   atomicCAS(w.status, kStatusOk, kStatusWaitTimeout | site);
   return false;
@@ -169,6 +189,8 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, uint32_t s
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // the issuing thread's bulk groups have finished READING shared memory
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the newest of the issuing thread's bulk groups have finished reading shared memory
+__device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // bring a tile into L2 only
 __device__ __forceinline__ void tma_prefetch_l2_5d(const CUtensorMap* tmap, int c0, int c1, int c2, int c3, int c4) {
