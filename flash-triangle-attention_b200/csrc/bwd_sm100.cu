@@ -260,6 +260,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tma_prefetch_desc(&tmDQ);
         tma_prefetch_desc(&tmPlane);
       }
+      // K/V/Q/dO tiles stream through L2 (each is read within a short window and never again);
+      // the bias tiles are re-read by every group and stay
+      const uint64_t pol_stream = l2_policy_evict_first(), pol_keep = l2_policy_evict_last();
       bool ok = true;
       int tt = 0, nb = 0;
       for (int n = 0; n < ngroups && ok; ++n) {
@@ -271,9 +274,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (elect_one()) {
           mbar_expect_tx(bar(C::B_KVFULL), Gc * 2 * C::TILE_B);
           for (int g = 0; g < Gc; ++g) {
-            tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL), 0, kb * 128, i0 + g, h, b);
-            tma_load_5d(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL), 0, kb * 128,
-                        i0 + g, h, b);
+            tma_load_5d_hint(smem_u32(sKV + g * 2 * C::TILE_B), &tmK, bar(C::B_KVFULL), 0, kb * 128, i0 + g, h, b,
+                             pol_stream);
+            tma_load_5d_hint(smem_u32(sKV + g * 2 * C::TILE_B + C::TILE_B), &tmV, bar(C::B_KVFULL), 0, kb * 128,
+                             i0 + g, h, b, pol_stream);
           }
           // K/V of the next group are read by no other CTA: bring them into L2 a whole group ahead
           if (n + 1 < ngroups) {
@@ -292,10 +296,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (elect_one()) {
             // transposed bias: innermost coordinate = query, then key
             mbar_expect_tx(bar(C::B_BIASFULL + bs), C::BIAS_B);
-            tma_load_4d(smem_u32(sBias + bs * C::BIAS_B), &tmBiasT, bar(C::B_BIASFULL + bs), jb * 128,
-                        kb * 128, h, b);
-            tma_load_4d(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBiasT, bar(C::B_BIASFULL + bs),
-                        jb * 128 + 64, kb * 128, h, b);
+            tma_load_4d_hint(smem_u32(sBias + bs * C::BIAS_B), &tmBiasT, bar(C::B_BIASFULL + bs), jb * 128,
+                             kb * 128, h, b, pol_keep);
+            tma_load_4d_hint(smem_u32(sBias + bs * C::BIAS_B + 16384), &tmBiasT, bar(C::B_BIASFULL + bs),
+                             jb * 128 + 64, kb * 128, h, b, pol_keep);
           }
           for (int g = 0; g < Gc; ++g, ++tt) {
             const int s = tt % C::NQ;
@@ -305,8 +309,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (elect_one()) {
               uint8_t* st = sQDO + s * C::STAGE_B;
               mbar_expect_tx(bar(C::B_QDOFULL + s), 2 * C::TILE_B + 2048);
-              tma_load_5d(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
-              tma_load_5d(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b);
+              tma_load_5d_hint(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b, pol_stream);
+              tma_load_5d_hint(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b,
+                               pol_stream);
               const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B), p.lse + roff, 512, bar(C::B_QDOFULL + s));
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.lse + p.stat_stride + roff, 512,
@@ -457,6 +462,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       //    (128 keys x 32 queries) written into the bias stage that has just been used up - the two
       //    warpgroups of a query half take turns in that half's 16 KB - and added to (first group:
       //    stored into) this CTA's private key-major plane.
+      // The planes (a few tens of MB, added to once per group) must stay in L2 between groups: with
+      // default priority the dQ stream evicts them and every addition becomes a DRAM read + write.
+      const uint64_t pol_keep = l2_policy_evict_last();
       bool ok = true;
       int k = 0, nb = 0;  // dQ tiles / query blocks so far
       auto dq_event = [&](int irow, int jblk) -> bool {
@@ -496,8 +504,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               const uint32_t src = smem_u32(sDS + hh * 16384);
               const int qcol = jb * 128 + (2 * hh + 1) * 32;
               if (!(FTA_EXP_PLANE_OUT)) continue;
-              if (n == 0) tma_store_2d(&tmPlane, src, qcol, prow);
-              else tma_reduce_add_2d(&tmPlane, src, qcol, prow);
+              if (n == 0) tma_store_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
+              else tma_reduce_add_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
             }
             bulk_commit_group();
           }
@@ -511,8 +519,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               const uint32_t src = smem_u32(sBias + bs * C::BIAS_B + hh * 16384);
               const int qcol = jb * 128 + (2 * hh) * 32;
               if (!(FTA_EXP_PLANE_OUT)) continue;
-              if (n == 0) tma_store_2d(&tmPlane, src, qcol, prow);
-              else tma_reduce_add_2d(&tmPlane, src, qcol, prow);
+              if (n == 0) tma_store_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
+              else tma_reduce_add_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
             }
             bulk_commit_group();
             bulk_wait_read_le1();  // the older group (dS tile) has been read

@@ -235,6 +235,53 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tma
 }
 
 // ----------------------------------------------------------------------------------
+// L2 eviction priorities for TMA traffic: `evict_last` keeps a small, often re-used working set
+// (partial-sum planes, the bias) resident while `evict_first` data (tiles read once) streams past
+// ----------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void tma_load_5d_hint(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int c0,
+                                                 int c1, int c2, int c3, int c4, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3), "r"(c4), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d_hint(uint32_t dst, const CUtensorMap* tmap, uint32_t bar, int c0,
+                                                 int c1, int c2, int c3, uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+      "r"(c3), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d_hint(const CUtensorMap* tmap, uint32_t src, int c0, int c1,
+                                                       uint64_t pol) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "l"(pol)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tmap, uint32_t src, int c0, int c1,
+                                                  uint64_t pol) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1), "l"(pol)
+      : "memory");
+}
+
+// ----------------------------------------------------------------------------------
 // tensor memory (TMEM) allocation: executed by one full warp
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result_addr, uint32_t ncols) {
