@@ -34,8 +34,8 @@ import numpy as np  # noqa: E402
 WORKLOAD = "ns_l768"
 METRIC = "fwd+bwd TFLOP/s, fused triangle attention B=1 H=4 L=768 D=32 bf16"
 # DRAM bytes (read + write) of ONE launch of the backward kernel at the full workload, from the
-# ncu capture summarised in profiles/bwd_kernel_ns_l768.md (None until measured).
-BWD_KERNEL_DRAM_BYTES = None
+# ncu capture summarised in profiles/bwd_kernel_ns_l768_dram.md.
+BWD_KERNEL_DRAM_BYTES = 1112545536 + 1069305856
 
 
 def _peaks():
