@@ -34,7 +34,7 @@ import numpy as np  # noqa: E402
 WORKLOAD = "ns_l768"
 METRIC = "fwd+bwd TFLOP/s, fused triangle attention B=1 H=4 L=768 D=32 bf16"
 # DRAM bytes (read + write) of ONE launch of the backward kernel at the full workload, from the
-# ncu capture summarised in profiles/bwd_kernel_ns_l768_dram.md.
+# one-pass ncu capture of that launch (dram__bytes_read.sum + dram__bytes_write.sum).
 BWD_KERNEL_DRAM_BYTES = 1112545536 + 1069305856
 
 
