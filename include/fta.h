@@ -107,7 +107,7 @@ FTA_API int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, cons
 FTA_API size_t fta_bwd_workspace_bytes(const FtaProblem* prob);
 
 /* Number of partial dBias planes the backward kernel produces for `prob` (each plane is
- * the sum of dS over a fixed group of consecutive L1 rows; they are summed in plane order). */
+ * the sum of dS over a fixed subset of the L1 rows; they are summed in plane order). */
 FTA_API int fta_bwd_num_planes(const FtaProblem* prob);
 
 /* Backward pass. Replaces the `_attn_bwd` launch and the `zeros_like` dBias buffer of
