@@ -780,6 +780,58 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if ((warp & 3) == 0) FTA_STAMP(qd, 7, tt);
         }
         if (!ok) break;
+        if (jb == nq - 1) {
+          // ---- group epilogue, before the dBias boxes so that the dK / dV stores are not queued
+          // behind their reductions: last dQ tile, then dK / dV of the G rows
+          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 0, n);
+          FTA_PROG(0x55, n);
+          ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
+          if (!ok) break;
+          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 1, n);
+          tc_fence_after_sync();
+          {
+            FTA_PROG(0x56, tt);
+            ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int pt = nq * Gc - 1;
+            ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, true);
+            if (!ok) break;
+          }
+          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 2, n);
+          {
+            // half 0 stores dV, half 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518); the two
+            // warpgroups of a half take alternate rows of the group
+            const long long* sd = (wh == 0) ? p.sdv : p.sdk;
+            uint16_t* base = reinterpret_cast<uint16_t*>(wh == 0 ? p.dv : p.dk) + b * sd[0] + h * sd[1] +
+                             static_cast<long long>(kb * 128 + key) * sd[3];
+            const float mul = (wh == 0) ? 1.0f : p.scale;
+            for (int g = sub; g < Gc; g += 2) {
+              uint16_t* optr = base + static_cast<long long>(i0 + g) * sd[2];
+              const uint32_t ta = tbase + C::TM_ACC + g * 2 * kD + (wh == 0 ? kD : 0) + lane_off;
+    #pragma unroll
+              for (int c = 0; c < kD / 32; ++c) {
+                uint32_t av[32];
+                tmem_ld32(ta + c * 32, av);
+                tmem_ld_wait();
+    #pragma unroll
+                for (int v4 = 0; v4 < 4; ++v4) {
+                  uint4 ov;
+                  ov.x = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 0]) * mul, __uint_as_float(av[v4 * 8 + 1]) * mul);
+                  ov.y = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 2]) * mul, __uint_as_float(av[v4 * 8 + 3]) * mul);
+                  ov.z = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 4]) * mul, __uint_as_float(av[v4 * 8 + 5]) * mul);
+                  ov.w = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 6]) * mul, __uint_as_float(av[v4 * 8 + 7]) * mul);
+                  *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
+                }
+              }
+            }
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::B_ACCFREE));
+          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 3, n);
+        }
+        if (!ok) break;
         // ---- dBias of this query block: the sums go to the store warp as 16 KB boxes parked in
         // shared memory that is idle at this point. The first warpgroup of a half uses that half's
         // part of the bias stage just used up (free once both warpgroups of the half have arrived
@@ -807,54 +859,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if ((warp & 3) == 0) FTA_STAMP(6 + qd, 1, nb);
       }
       if (!ok) break;
-      // ---- group epilogue: last dQ tile, then dK / dV of the G rows
-      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 0, n);
-      FTA_PROG(0x55, n);
-      ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
-      if (!ok) break;
-      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 1, n);
-      tc_fence_after_sync();
-      {
-        FTA_PROG(0x56, tt);
-        ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
-        if (!ok) break;
-        tc_fence_after_sync();
-        const int pt = nq * Gc - 1;
-        ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, true);
-        if (!ok) break;
-      }
-      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 2, n);
-      {
-        // half 0 stores dV, half 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518); the two
-        // warpgroups of a half take alternate rows of the group
-        const long long* sd = (wh == 0) ? p.sdv : p.sdk;
-        uint16_t* base = reinterpret_cast<uint16_t*>(wh == 0 ? p.dv : p.dk) + b * sd[0] + h * sd[1] +
-                         static_cast<long long>(kb * 128 + key) * sd[3];
-        const float mul = (wh == 0) ? 1.0f : p.scale;
-        for (int g = sub; g < Gc; g += 2) {
-          uint16_t* optr = base + static_cast<long long>(i0 + g) * sd[2];
-          const uint32_t ta = tbase + C::TM_ACC + g * 2 * kD + (wh == 0 ? kD : 0) + lane_off;
-#pragma unroll
-          for (int c = 0; c < kD / 32; ++c) {
-            uint32_t av[32];
-            tmem_ld32(ta + c * 32, av);
-            tmem_ld_wait();
-#pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 ov;
-              ov.x = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 0]) * mul, __uint_as_float(av[v4 * 8 + 1]) * mul);
-              ov.y = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 2]) * mul, __uint_as_float(av[v4 * 8 + 3]) * mul);
-              ov.z = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 4]) * mul, __uint_as_float(av[v4 * 8 + 5]) * mul);
-              ov.w = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 6]) * mul, __uint_as_float(av[v4 * 8 + 7]) * mul);
-              *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
-            }
-          }
-        }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(C::B_ACCFREE));
-      if ((warp & 3) == 0) FTA_STAMP(10 + qd, 3, n);
     }
   }
 
