@@ -452,9 +452,13 @@ __device__ __forceinline__ void reg_dec() {
 // small numeric helpers
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ float fast_exp2(float x) {
+#ifdef FTA_EXP_NOEX2
+  return x * 0.5f;  // timing study only
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {

@@ -142,11 +142,46 @@ class _attention(torch.autograd.Function):
         return dq, dk, dv, db, None, None
 
 
-def attention(q, k, v, b_pw, sm_scale, group=None):
+def attention(q, k, v, b_pw, sm_scale, group=None, key_mask=None):
     """Fused triangle attention: ``softmax(q k^T * sm_scale + b_pw) v`` for q, k, v of shape
     (B, H, L1, L2, D) and a pair bias (B, H, L2, L2) shared by the L1 rows; differentiable in
-    q, k, v and b_pw (dBias is summed over L1). See the module docstring."""
-    return _attention.apply(q, k, v, b_pw, sm_scale, group)
+    q, k, v and b_pw (dBias is summed over L1). See the module docstring.
+
+    Two extensions of the reference's call (flash_tt_attn.py:663), both keyword-only in spirit:
+    ``key_mask`` (bool, broadcastable to (B, 1, 1, L2) or of shape (B, L2); True = attend) removes
+    keys without the caller building a -1e9 bias, and ``L2`` need not be a multiple of 128.
+    Either one goes through a padded copy of the inputs (L2 rounded up to 128, padded / masked
+    keys get a large negative bias, padded queries are cropped from the result and receive zero
+    gradient); the kernels themselves always see whole 128-key tiles."""
+    L2 = q.shape[3]
+    if key_mask is None and L2 % 128 == 0:
+        return _attention.apply(q, k, v, b_pw, sm_scale, group)
+    return _attention_padded(q, k, v, b_pw, sm_scale, group, key_mask)
+
+
+def _attention_padded(q, k, v, b_pw, sm_scale, group, key_mask):
+    B, H, L1, L2, D = q.shape
+    Lp = (L2 + 127) // 128 * 128
+    pad = Lp - L2
+    # the most negative bias that is still finite in the bias dtype and keeps exp2 at exactly 0
+    neg = -6.0e4 if b_pw.dtype == torch.float16 else -1.0e9
+    bias = b_pw
+    if key_mask is not None:
+        km = key_mask
+        if km.dim() == 2:
+            km = km[:, None, None, :]
+        assert km.dtype == torch.bool and km.shape[-1] == L2
+        bias = torch.where(km.expand(B, H, L2, L2) if km.dim() == 4 else km, bias,
+                           torch.full((), neg, dtype=bias.dtype, device=bias.device))
+    if pad:
+        # F.pad is differentiable: gradients of the padded parts are dropped on the way back
+        F = torch.nn.functional
+        q = F.pad(q, (0, 0, 0, pad))
+        k = F.pad(k, (0, 0, 0, pad))
+        v = F.pad(v, (0, 0, 0, pad))
+        bias = F.pad(bias, (0, pad, 0, pad), value=neg)
+    out = _attention.apply(q, k, v, bias, sm_scale, group)
+    return out[:, :, :, :L2] if pad else out
 
 
 def reference_tt_attn(q, k, v, b, sm_scale):

@@ -207,3 +207,56 @@ def test_full_size_metric_shape_properties():
     o = fta.attention(t["q"], t["k"], ones, t["bias"], w.sm_scale)
     fta.check_device_status()
     assert float((o.float() - 1.0).abs().max()) <= 1e-2
+
+
+
+def test_ending_node_views_need_no_copy_in_forward_and_backward():
+    """Ending-node orientation passed as transposed VIEWS (D stays contiguous): the tensor maps and
+    the output stores take the strides as they are; values and gradients equal the copied form."""
+    w = workloads.Workload("t", 1, 2, 128, 256, 32, "bf16", seed=11)
+    x = workloads.make_inputs(w)
+    t = {k: torch.from_numpy(x[k]).cuda().to(torch.bfloat16) for k in x if k != "mask"}
+    # stored (B,H,L2,L1,D); the op sees (B,H,L1,L2,D) through transpose(2,3)
+    res = []
+    for copy in (True, False):
+        leaf = {k: t[k].transpose(2, 3).contiguous().clone().requires_grad_(True) for k in ("q", "k", "v")}
+        bias = t["bias"].clone().requires_grad_(True)
+        args = [leaf[k].transpose(2, 3) for k in ("q", "k", "v")]
+        if copy:
+            args = [a.contiguous() for a in args]
+        else:
+            assert not args[0].is_contiguous()
+        o = fta.attention(*args, bias, w.sm_scale)
+        o.backward(t["do"])
+        fta.check_device_status()
+        res.append((o.detach(), leaf["q"].grad, leaf["k"].grad, leaf["v"].grad, bias.grad))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+
+
+
+def test_key_mask_and_ragged_l2_through_padding():
+    """L2 = 200 (not a multiple of 128) with a boolean key mask: equal to the oracle on the same
+    problem written with a -1e9 bias; masked keys receive exactly zero dBias columns."""
+    B, H, L1, L2, D = 1, 2, 3, 200, 32
+    g = torch.Generator().manual_seed(7)
+    q, k, v, do = [torch.randn(B, H, L1, L2, D, generator=g).to(torch.bfloat16) for _ in range(4)]
+    bias = torch.randn(B, H, L2, L2, generator=g).to(torch.bfloat16)
+    mask = torch.rand(B, L2, generator=g) > 0.2
+    mask[:, 0] = True
+    scale = D ** -0.5
+    leaves = [a.cuda().requires_grad_(True) for a in (q, k, v, bias)]
+    o = fta.attention(*leaves, scale, key_mask=mask.cuda())
+    o.backward(do.cuda())
+    fta.check_device_status()
+    assert o.shape == (B, H, L1, L2, D)
+    bm = torch.where(mask[:, None, None, :], bias.float(), torch.tensor(-1.0e9))
+    ref = npo.forward_backward(q.float().numpy(), k.float().numpy(), v.float().numpy(), bm.numpy(),
+                               do.float().numpy(), scale)
+    got = {"o": o, "dq": leaves[0].grad, "dk": leaves[1].grad, "dv": leaves[2].grad, "dbias": leaves[3].grad}
+    for name in ("o", "dq", "dk", "dv", "dbias"):
+        a = got[name].detach().float().cpu().numpy()
+        assert npo.max_abs(a, ref[name]) <= MAX_ABS, name
+        assert npo.rel_l2(a, ref[name]) <= REL_L2 * (2 if name == "dbias" else 1), name
+    dead = ~mask[0].numpy()
+    assert np.all(got["dbias"].float().cpu().numpy()[0][:, :, dead] == 0.0)
