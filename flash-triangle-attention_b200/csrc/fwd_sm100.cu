@@ -130,8 +130,11 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int nunits = (ngroups - static_cast<int>(blockIdx.y) + static_cast<int>(gridDim.y) - 1) /
                      static_cast<int>(gridDim.y);
   auto unit_i0 = [&](int u) { return (static_cast<int>(blockIdx.y) + u * static_cast<int>(gridDim.y)) * G; };
-  // rows processed in a unit (an odd tail is padded with a zero row)
-  auto unit_gp = [&](int u) { return (min(G, p.L1 - unit_i0(u)) + 1) & ~1; };
+  // Every unit processes G rows: a short last group is padded with rows past L1, which the TMA
+  // loads fill with zeros and the epilogue does not store.
+  // (kept a run-time value: as a compile-time constant it changes the code the compiler generates
+  // for the softmax loop, measurably for the worse)
+  auto unit_gp = [&](int u) { return unit_i0(u) < p.L1 ? G : 0; };
 #ifdef FTA_TRACE
   const WaitCtx w{smem_u32(abort_flag), p.status, nullptr};
 #else
@@ -371,6 +374,14 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = need ? fast_exp2((m_old - m_safe) * kLog2e) : 1.0f;
         if (kb > 0 && __any_sync(0xffffffffu, need)) {
+          // The rescale reads and writes the O accumulator of this row, so the row's previous PV MMA
+          // must be done. With two or more rows per warpgroup that was waited for a tile ago; with a
+          // single row the previous tile WAS this row.
+          if constexpr (G == 2) {
+            ok = mbar_wait_warp(bar(C::B_PVDONE + wg), (n - 1) & 1, w, 13);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
 #pragma unroll
           for (int c = 0; c < kD / 32; ++c) {
             uint32_t orr[32];
