@@ -82,6 +82,9 @@ __device__ unsigned long long g_progress[128];
 #ifndef FTA_EXP_DUMP
 #define FTA_EXP_DUMP 4
 #endif
+#ifndef FTA_EXP_PH16
+#define FTA_EXP_PH16 0  // 1: phase 2 reads P from a separate half-precision copy (bf16 inputs)
+#endif
 #ifndef FTA_EXP_DQ_OUT
 #define FTA_EXP_DQ_OUT true
 #endif
@@ -662,7 +665,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                       y0, y1);
                   const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
                   pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                  ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                  ph[ch * 4 + e] = (kBf16 && FTA_EXP_PH16) ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
                 }
               }
             }
@@ -693,7 +696,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 un2(fma2(add2(x, nm2[e]), log2e2, nl2[e]), y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
                 pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                ph[ch * 4 + e] = (kBf16 && FTA_EXP_PH16) ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
               }
             }
           }
@@ -725,7 +728,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               for (int e = 0; e < 4; ++e) {
                 const int idx = c8 * 8 + 2 * e;
                 float p0, p1, ds0, ds1;
-                unpack2<false>(ph[ch * 4 + e], p0, p1);
+                unpack2<(kBf16 && !FTA_EXP_PH16)>(ph[ch * 4 + e], p0, p1);
                 const f32x2 u = fma2(del2[e], neg1_2, mk2(__uint_as_float(dv[idx]), __uint_as_float(dv[idx + 1])));
                 const f32x2 ds = mul2(mk2(p0, p1), u);
                 acc[ch * 4 + e] = add2(acc[ch * 4 + e], ds);
