@@ -12,22 +12,26 @@
 //   dV  += P^T dO, dK += dS^T Q                        (A operand read from TMEM)
 //   dQ   = dS K                                        (dS staged in smem, M-major)
 //
-// The tile is split in two 64-query halves, one per compute warpgroup, each with its own
-// S^T / dP^T columns and barriers, so the tensor core works on one half while the CUDA cores
-// work on the other. The bias is read from a transposed copy (key-major) so that the thread
-// that owns a key row reads its 64 query columns with 16-byte shared-memory loads.
+// The tile is split in two 64-query halves, each with its own S^T / dP^T columns and barriers
+// and two compute warpgroups (one 32-query quarter each), so the tensor core works on one half
+// while the CUDA cores work on the other. The bias is read from a transposed copy (key-major)
+// so that the thread that owns a key row reads its query columns with 16-byte shared-memory loads.
 //
-// dBias: each thread owns one key column and 64 query rows of the (jb,kb) tile and sums dS
-// (float32, before rounding) over the G rows in registers; the sums are then added to the
-// CTA's PRIVATE float32 plane (plane index r) with `red.global.add.f32`. A plane element is
-// only ever touched by one thread of one CTA, in program order, so the result is bit-exact
-// run to run; the planes are summed in fixed order by the finalise kernel.
-// dQ leaves the CTA as float32 reductions into a zero-initialised buffer (sum over key blocks).
+// dBias: each thread owns one key column and 32 query rows of the (jb,kb) tile and sums dS
+// (float32, before rounding) over the G rows in registers. At the end of a query block each
+// warpgroup parks its 16 KB box of sums in shared memory that is idle at that moment and the
+// store warp adds it to the CTA's PRIVATE float32 plane (plane index r, key-major) with a TMA tile
+// reduction. A plane element is only ever touched by one CTA, one addition per group, each
+// completed before the next, so the result is bit-exact run to run; the planes are summed in
+// fixed order by the finalise kernel.
+// dQ leaves the CTA the same way: TMEM -> shared memory -> TMA reduction into a zero-initialised
+// float32 buffer (sum over key blocks). Every route out of an SM carries about 20 bytes per
+// cycle; the TMA route costs the compute warps nothing but the shared-memory writes.
 //
-//   warp 0     : tcgen05 issuer (lowest warp id: the scheduler prefers older warps)
-//   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : dQ store warp (TMA reductions)
+//   warp 0     : tcgen05 issuer (S^T, dP^T, dV, dK; lowest warp id: the scheduler prefers older warps)
+//   warp 1     : TMA producer        warp 2 : issuer of the dQ MMAs        warp 3 : store warp (TMA reductions)
 //   warps 4-19 : four compute warpgroups, one 32-query quarter of the tile each; quarters 0-1
-//                (half 0) also store dV, quarters 2-3 (half 1) store dK; each reduces a quarter of dQ
+//                (half 0) also store dV, quarters 2-3 (half 1) store dK
 // Producer and issuer loops run warp-uniformly; one elected lane issues the TMA / MMA.
 #include "fta_kernels.h"
 #include "tc05.cuh"

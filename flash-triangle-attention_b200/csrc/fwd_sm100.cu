@@ -1,9 +1,11 @@
 // Forward triangle attention for sm_100a: O = softmax(sm_scale * q k^T + bias) v and the
 // softmax statistics (row max and log2 of the row sum), the work of the reference's `_attn_fwd` (flash_tt_attn.py:128-264).
 //
-// One CTA owns a 128-query block `jb` of a group of up to G consecutive L1 rows of one
-// (b,h). It walks the key blocks once (outer loop) and, inside, the G rows (inner loop), so
-// that one 128x128 bias tile staged in shared memory serves G score tiles:
+// One CTA owns a 128-query block `jb` of one (b,h) and walks a residue class of the groups of G
+// consecutive L1 rows back to back (loads and MMAs of the next group start while the softmax
+// warps finish the current one). Within a group it walks the key blocks once (outer loop) and,
+// inside, the G rows (inner loop), so that one 128x128 bias tile staged in shared memory serves
+// G score tiles:
 //
 //   warp 0      : tcgen05 issuer (S = Q K^T into TMEM, O += P V with P read from TMEM)
 //   warp 1      : TMA producer  (Q tiles once, K/V ring, bias double buffer)
