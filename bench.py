@@ -36,6 +36,8 @@ METRIC = "fwd+bwd TFLOP/s, fused triangle attention B=1 H=4 L=768 D=32 bf16"
 # DRAM bytes (read + write) of ONE launch of the backward kernel at the full workload, from the
 # one-pass ncu capture of that launch (dram__bytes_read.sum + dram__bytes_write.sum).
 BWD_KERNEL_DRAM_BYTES = 1112545536 + 1069305856
+# L1 rows per block of the end-to-end leg (host tensors streamed through the GPU)
+E2E_BLOCK_ROWS = int(os.environ.get("FTA_E2E_BLOCK_ROWS", "96"))
 
 
 def _peaks():
@@ -282,17 +284,12 @@ def main():
     d2h = sum(v.numel() * v.element_size() for v in out_host.values()) + db_host.numel() * db_host.element_size()
     grp = dist.group.WORLD if sharded else None
 
+    out_host["dbias"] = db_host
+
     def e2e_step():
-        t_ = {k: host[k].to(dev, non_blocking=True) for k in host}
-        for k in ("q", "k", "v", "bias"):
-            t_[k].requires_grad_()
-        out = fta.attention(t_["q"], t_["k"], t_["v"], t_["bias"], scale, group=grp)
-        out.backward(t_["do"])
-        out_host["o"].copy_(out.detach(), non_blocking=True)
-        out_host["dq"].copy_(t_["q"].grad, non_blocking=True)
-        out_host["dk"].copy_(t_["k"].grad, non_blocking=True)
-        out_host["dv"].copy_(t_["v"].grad, non_blocking=True)
-        db_host.copy_(t_["bias"].grad, non_blocking=True)
+        # the library's host-memory entry point: blocks of L1 rows double-buffered through the GPU,
+        # copies in / kernels / copies out on three streams
+        fta.attention_fwd_bwd_streamed(host, scale, out_host, block_rows=E2E_BLOCK_ROWS, device=dev, group=grp)
 
     if args.no_e2e:
         e2e_steps = 0

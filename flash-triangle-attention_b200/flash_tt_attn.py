@@ -31,7 +31,8 @@ import torch
 import _cabi
 from _cabi import FtaProblem, check, t4, t5
 
-__all__ = ["attention", "reference_tt_attn", "check_device_status", "last_dbias_f32"]
+__all__ = ["attention", "attention_fwd_bwd_streamed", "reference_tt_attn", "check_device_status",
+           "last_dbias_f32"]
 
 _DEBUG = os.environ.get("FTA_DEBUG", "0") == "1"
 _status_words = {}
@@ -197,3 +198,74 @@ def shard_rows(L1: int, rank: int, world: int) -> slice:
     """Contiguous block of L1 rows owned by ``rank`` (rows are independent problems)."""
     per = (L1 + world - 1) // world
     return slice(min(L1, rank * per), min(L1, (rank + 1) * per))
+
+
+def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, group=None):
+    """Forward + backward for tensors that live in (pinned) HOST memory, streamed through the GPU
+    in blocks of L1 rows: the copies of block i+1 (host to device) and of the results of block
+    i-1 (device to host) run on their own streams while the kernels of block i run, so a call
+    costs about max(copy in, copy out, compute) instead of their sum. Rows of L1 are independent
+    problems; only dBias couples them, and it is summed over the blocks in float32, in block
+    order, and rounded once.
+
+    host : dict with ``q, k, v, do`` of shape (B, H, L1, L2, D) and ``bias`` (B, H, L2, L2), CPU
+           tensors (pinned for asynchronous copies), 16-bit dtype
+    out  : dict with ``o, dq, dk, dv`` like ``q`` and ``dbias`` like ``bias``, CPU tensors (pinned)
+    group: with a process group, ``host`` holds this rank's rows and dBias is all-reduced once.
+    Returns after everything has arrived in ``out``.
+    """
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    q_h, k_h, v_h, do_h, b_h = host["q"], host["k"], host["v"], host["do"], host["bias"]
+    B, H, L1, L2, D = q_h.shape
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    nblk = (L1 + block_rows - 1) // block_rows
+    bufs = [{k: torch.empty((B, H, min(block_rows, L1), L2, D), dtype=q_h.dtype, device=dev)
+             for k in ("q", "k", "v", "do")} for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    s_in.wait_stream(cur)
+    with torch.cuda.stream(s_in):
+        bias = b_h.to(dev, non_blocking=True)
+    db32 = torch.zeros((B, H, L2, L2), dtype=torch.float32, device=dev)
+    keep = []  # results in flight to the host
+
+    def copy_rows(dst, src, r0, r1):
+        # per (b, h) the block of rows is contiguous on both sides: plain asynchronous copies
+        for b_ in range(B):
+            for h_ in range(H):
+                dst[b_, h_, : r1 - r0].copy_(src[b_, h_, r0:r1], non_blocking=True)
+
+    for blk in range(nblk):
+        slot = blk & 1
+        r0, r1 = blk * block_rows, min(L1, (blk + 1) * block_rows)
+        with torch.cuda.stream(s_in):
+            if blk >= 2:
+                s_in.wait_event(ev_comp[slot])  # the kernels of block blk-2 have read this slot
+            for name, src in (("q", q_h), ("k", k_h), ("v", v_h), ("do", do_h)):
+                copy_rows(bufs[slot][name], src, r0, r1)
+            ev_in[slot].record(s_in)
+        cur.wait_event(ev_in[slot])
+        n = r1 - r0
+        qd, kd, vd = (bufs[slot][name][:, :, :n].detach().requires_grad_() for name in ("q", "k", "v"))
+        bias_leaf = bias.detach().requires_grad_()
+        o = _attention.apply(qd, kd, vd, bias_leaf, sm_scale, None)
+        o.backward(bufs[slot]["do"][:, :, :n])
+        db32 += _last["dbias_f32"]
+        ev_comp[slot].record(cur)
+        res = {"o": o.detach(), "dq": qd.grad, "dk": kd.grad, "dv": vd.grad}
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[slot])
+            for name, t in res.items():
+                t.record_stream(s_out)
+                for b_ in range(B):
+                    for h_ in range(H):
+                        out[name][b_, h_, r0:r1].copy_(t[b_, h_], non_blocking=True)
+        keep.append(res)
+    if group is not None:
+        torch.distributed.all_reduce(db32, op=torch.distributed.ReduceOp.SUM, group=group)
+    out["dbias"].copy_(db32.to(b_h.dtype), non_blocking=True)
+    _last["dbias_f32"] = db32
+    cur.wait_stream(s_out)
+    torch.cuda.synchronize(dev)
+    check_device_status(dev)
