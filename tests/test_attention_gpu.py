@@ -284,3 +284,69 @@ def test_streamed_host_entry_point_matches_the_device_path():
     ref = fta.last_dbias_f32()
     assert float((db_streamed - ref).abs().max()) <= 1e-4 * float(ref.abs().max()) + 1e-5
     assert npo.rel_l2(out["dbias"].float().numpy(), ref.cpu().numpy()) <= 5e-3
+
+
+def _device_inputs(w, dtype, with_do=True):
+    """Full-size tensors drawn on the device (host generation of GiB-sized tensors is too slow for
+    a test); the checks below copy the sampled rows back and hand the same values to the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(w.seed)
+    shape = (w.B, w.H, w.L1, w.L2, w.D)
+    t = {k: (torch.randn(shape, device="cuda", dtype=torch.float32, generator=g) * w.qkv_std).to(dtype)
+         for k in ("q", "k", "v")}
+    if with_do:
+        t["do"] = torch.randn(shape, device="cuda", dtype=torch.float32, generator=g).to(dtype)
+    t["bias"] = (torch.randn((w.B, w.H, w.L2, w.L2), device="cuda", dtype=torch.float32, generator=g)
+                 * w.bias_std).to(dtype)
+    return t
+
+
+def _rows_to_numpy(t, sl):
+    return {k: (v if k == "bias" else v[:, :, sl]).float().cpu().numpy() for k, v in t.items()}
+
+
+def test_c4_inference_shape_forward_only():
+    """B1 H4 L1024 D32 bf16, forward only (q,k,v std 1/sqrt(D), bias std 2): sampled L1 rows against
+    the oracle and the V = 1 property over the whole tensor."""
+    w = workloads.WORKLOADS["c4_infer_l1024"]
+    t = _device_inputs(w, torch.bfloat16, with_do=False)
+    with torch.no_grad():
+        o = fta.attention(t["q"], t["k"], t["v"], t["bias"], w.sm_scale)
+        ones = fta.attention(t["q"], t["k"], torch.ones_like(t["v"]), t["bias"], w.sm_scale)
+    fta.check_device_status()
+    assert float((ones.float() - 1.0).abs().max()) <= 1e-2
+    for i in (0, 511, 1023):
+        sl = slice(i, i + 1)
+        r = _rows_to_numpy(t, sl)
+        ref = c_oracle.forward(r["q"], r["k"], r["v"], r["bias"], w.sm_scale)
+        got = o[:, :, sl].float().cpu().numpy()
+        assert npo.max_abs(got, ref) <= MAX_ABS and npo.rel_l2(got, ref) <= REL_L2, i
+
+
+def test_c5_long_sequence_training_shape_sampled_rows():
+    """B1 H8 L2048 D64 bf16 (4 GiB per tensor), forward + backward: sampled L1 rows of O, dQ, dK,
+    dV against the oracle (they are per-row quantities) and the row sums of dBias (each dS row
+    sums to zero, so every row of dBias must too, relative to its absolute sum)."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 80 * 2 ** 30:
+        pytest.skip("needs about 70 GiB of device memory")
+    w = workloads.WORKLOADS["c5_train_l2048"]
+    t = _device_inputs(w, torch.bfloat16)
+    for k in ("q", "k", "v", "bias"):
+        t[k].requires_grad_()
+    o = fta.attention(t["q"], t["k"], t["v"], t["bias"], w.sm_scale)
+    o.backward(t["do"])
+    fta.check_device_status()
+    db32 = fta.last_dbias_f32()
+    rowsum = db32.double().sum(-1)
+    scale_ = db32.double().abs().sum(-1)
+    assert float((rowsum.abs() / scale_).max()) < 2e-3
+    got = {"o": o.detach(), "dq": t["q"].grad, "dk": t["k"].grad, "dv": t["v"].grad}
+    vals = {k: v.detach() for k, v in t.items()}
+    for i in (0, 1000, 2047):
+        sl = slice(i, i + 1)
+        r = _rows_to_numpy(vals, sl)
+        ref = c_oracle.forward_backward(r["q"], r["k"], r["v"], r["bias"], r["do"], w.sm_scale)
+        for k in ("o", "dq", "dk", "dv"):
+            a = got[k][:, :, sl].float().cpu().numpy()
+            assert npo.max_abs(a, ref[k]) <= MAX_ABS, (k, i, npo.max_abs(a, ref[k]))
+            assert npo.rel_l2(a, ref[k]) <= REL_L2, (k, i, npo.rel_l2(a, ref[k]))
