@@ -573,6 +573,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // reduce this warpgroup's quarter of the columns of one finished dQ tile (TMEM buffer `buf`)
     // into the float32 dQ accumulator; the four warpgroups share the work evenly
     int kdq = 0;  // dQ tiles handed to the store warp so far
+    int ring_slot = 0;
+    uint32_t ring_phase = 0;
     // `publish`: fence and tell the store warp here; otherwise the caller does both (it shares
     // the fence with its own shared-memory writes)
     auto reduce_dq = [&](int buf, int irow, int jblk, bool publish) -> bool {
@@ -624,13 +626,19 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if ((warp & 3) == 0) FTA_STAMP(6 + qd, 0, nb);
         const uint8_t* brow = sBias + bs * C::BIAS_B + wh * 16384 + key * 128;
         for (int g = 0; g < Gc; ++g, ++tt) {
-          const int s = tt % C::NQ;
+          // Q/dO ring slot and phase of tile tt (tt % NQ, (tt / NQ) & 1) kept as running counters
+          const int s = ring_slot;
+          const uint32_t ring_par = ring_phase;
+          if (++ring_slot == C::NQ) {
+            ring_slot = 0;
+            ring_phase ^= 1u;
+          }
           const uint8_t* st = sQDO + s * C::STAGE_B;
           if ((warp & 3) == 0) FTA_STAMP(qd, 0, tt);
           FTA_PROG(0x50, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
-          ok = mbar_wait_warp(bar(C::B_QDOFULL + s), (tt / C::NQ) & 1, w, 0x43);  // statistics visible
+          ok = mbar_wait_warp(bar(C::B_QDOFULL + s), ring_par, w, 0x43);  // statistics visible
           if (!ok) break;
           if ((warp & 3) == 0) FTA_STAMP(qd, 1, tt);
           tc_fence_after_sync();

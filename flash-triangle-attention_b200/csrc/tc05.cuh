@@ -155,6 +155,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 // Same, executed by a full converged warp; the outcome is made warp-uniform so that the
 // warp-collective tcgen05.ld / st that follow are executed by all lanes or by none.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& w, int site) {
+  // fast path: one poll and one vote, the outcome already warp-uniform
+  uint32_t all_ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "vote.sync.all.pred q, p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(all_ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  if (all_ok) return true;
   const bool ok = mbar_wait(bar, parity, w, site);
   return __all_sync(0xffffffffu, ok);
 }
