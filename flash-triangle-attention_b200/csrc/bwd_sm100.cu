@@ -2,8 +2,8 @@
 // `_attn_bwd` (flash_tt_attn.py:442-550) with each score tile visited ONCE (5 MMAs and one
 // exp2 per score instead of the reference's two passes).
 //
-// A CTA owns one key block `kb` of one (b,h) and a fixed residue class `r` of the groups of
-// G consecutive L1 rows (groups r, r+NP, r+2NP, ...). For each group it keeps K/V of the G
+// A CTA owns one key block `kb` of one (b,h) and the r-th of NP nearly equal blocks of consecutive
+// L1 rows, which it walks in groups of G rows. For each group it keeps K/V of the G
 // rows in shared memory and dK/dV of the G rows in TMEM, and walks the query blocks `jb`
 // (outer) and the G rows (inner):
 //
@@ -208,8 +208,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int r = (blockIdx.x / nkb) % p.NP;
   const int bh = blockIdx.x / (nkb * p.NP);
   const int b = bh / p.H, h = bh % p.H;
-  const int ngroups_total = (p.L1 + G - 1) / G;
-  const int ngroups = (ngroups_total - r + p.NP - 1) / p.NP;  // groups r, r+NP, ...
+  // This CTA's rows: the r-th of NP nearly equal blocks of consecutive L1 rows (sizes differ by at
+  // most one row, none empty since NP <= L1), walked in groups of G rows with a short last group.
+  const int row_begin = static_cast<int>(static_cast<long long>(r) * p.L1 / p.NP);
+  const int row_end = static_cast<int>(static_cast<long long>(r + 1) * p.L1 / p.NP);
+  const int ngroups = (row_end - row_begin + G - 1) / G;
 #ifdef FTA_TRACE
   const WaitCtx w{smem_u32(abort_flag), p.status, blockIdx.x == 0 ? g_trace_bwd + 15 * 512 : nullptr};
 #else
@@ -273,8 +276,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       bool ok = true;
       int tt = 0, nb = 0;
       for (int n = 0; n < ngroups && ok; ++n) {
-        const int i0 = (r + n * p.NP) * G;
-        const int Gc = min(G, p.L1 - i0);
+        const int i0 = row_begin + n * G;
+        const int Gc = min(G, row_end - i0);
         FTA_PROG(0x12, n);
         ok = mbar_wait_warp(bar(C::B_KVFREE), (n & 1) ^ 1, w, 0x21);
         if (!ok) break;
@@ -288,8 +291,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           // K/V of the next group are read by no other CTA: bring them into L2 a whole group ahead
           if (n + 1 < ngroups) {
-            const int i1 = (r + (n + 1) * p.NP) * G;
-            for (int g = 0; g < min(G, p.L1 - i1); ++g) {
+            const int i1 = row_begin + (n + 1) * G;
+            for (int g = 0; g < min(G, row_end - i1); ++g) {
               tma_prefetch_l2_5d(&tmK, 0, kb * 128, i1 + g, h, b);
               tma_prefetch_l2_5d(&tmV, 0, kb * 128, i1 + g, h, b);
             }
@@ -370,8 +373,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         __syncwarp();
       };
       for (int n = 0; n < ngroups && ok; ++n) {
-        const int i0 = (r + n * p.NP) * G;
-        const int Gc = min(G, p.L1 - i0);
+        const int i0 = row_begin + n * G;
+        const int Gc = min(G, row_end - i0);
         const int T = nq * Gc;
         FTA_PROG(0x25, n);
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32) &&
@@ -433,8 +436,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       bool ok = true;
       int tt = 0;
       for (int n = 0; n < ngroups && ok; ++n) {
-        const int i0 = (r + n * p.NP) * G;
-        const int Gc = min(G, p.L1 - i0);
+        const int i0 = row_begin + n * G;
+        const int Gc = min(G, row_end - i0);
         const int T = nq * Gc;
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x36);
         for (int t = 0; t < T && ok; ++t, ++tt) {
@@ -489,8 +492,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         return true;
       };
       for (int n = 0; n < ngroups && ok; ++n) {
-        const int i0 = (r + n * p.NP) * G;
-        const int Gc = min(G, p.L1 - i0);
+        const int i0 = row_begin + n * G;
+        const int Gc = min(G, row_end - i0);
         const int prow = (r * p.BH + bh) * p.L2 + kb * 128;  // first key row of this CTA's plane tile
         for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
           if constexpr (C::DQ_TMA) {
@@ -613,8 +616,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       return true;
     };
     for (int n = 0; n < ngroups && ok; ++n) {
-      const int i0 = (r + n * p.NP) * G;
-      const int Gc = min(G, p.L1 - i0);
+      const int i0 = row_begin + n * G;
+      const int Gc = min(G, row_end - i0);
       for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
         f32x2 acc[16];  // dBias sums: this key column x 32 query rows
 #pragma unroll
@@ -850,9 +853,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (!ok) break;
         // ---- dBias of this query block: the sums go to the store warp as 16 KB boxes parked in
         // shared memory that is idle at this point. The first warpgroup of a half uses that half's
-        // part of the bias stage just used up (free once both warpgroups of the half have arrived
-        // for the last tile's phase 2), the second one that half's part of the dS tile (free once
-        // the last dQ MMA has read it).
+        // part of the bias stage just used up (free once both warpgroups of the half have read
+        // their bias values; waiting for their phase-2 arrival rather than the earlier phase-1 one
+        // also keeps the two warpgroups of the half in step, which measures faster), the second
+        // one that half's part of the dS tile (free once the last dQ MMA has read it).
         FTA_PROG(0x53, nb);
         if (sub == 0) ok = mbar_wait_warp(bar(C::B_P2FULL + wh), (tt - 1) & 1, w, 0x49);
         else ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x4a);
@@ -953,7 +957,7 @@ extern "C" __attribute__((visibility("default"))) int fta_progress_read(unsigned
 
 int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
 
-// Number of private dBias planes == number of row-group residue classes. Chosen so that the
+// Number of private dBias planes == number of row blocks per (b,h,key block). Chosen so that the
 // grid (B*H * L2/128 * NP CTAs, one per SM at a time) fills whole waves of the device with
 // chains of nearly equal length, with as few planes as that allows.
 int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms) {
@@ -964,9 +968,9 @@ int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms) {
   auto efficiency = [&](int np) {
     const long long ctas = base * np;
     const long long waves = (ctas + num_sms - 1) / num_sms;
-    const int chain = (ngroups + np - 1) / np;  // longest chain
-    // time ~ waves * chain ; work ~ base * ngroups / num_sms
-    return (static_cast<double>(base) * ngroups / num_sms) / (static_cast<double>(waves) * chain);
+    const int chain = (L1 + np - 1) / np;  // rows of the longest chain
+    // time ~ waves * chain ; work ~ base * L1 / num_sms
+    return (static_cast<double>(base) * L1 / num_sms) / (static_cast<double>(waves) * chain);
   };
   double best_eff = -1.0;
   for (int np = 1; np <= np_max; ++np) best_eff = efficiency(np) > best_eff ? efficiency(np) : best_eff;
