@@ -6,9 +6,11 @@
 One "step" = one forward + backward pass of fused triangle attention over one batch of
 synthetic input: the headline shape B=1, H=4, L1=L2=768, D=32, bf16 (workload ``ns_l768``),
 811.75 GFLOP per step by the metric's model (4*B*H*L1*L2^2*D forward, 2.5x that backward).
-With N > 1 (launched by torchrun, one rank per GPU) the L1 rows are sharded over the ranks,
-the bias is replicated, and the backward all-reduces the float32 dBias over NCCL; the value is
-whole-problem FLOPs / max-over-ranks device time (total work fixed: strong scaling).
+With N > 1 (launched by torchrun, one rank per GPU) the problem is split heads first, L1 rows second:
+ranks that own different heads exchange nothing (a head's dBias is complete on its rank); ranks that
+share a head own blocks of its L1 rows and all-reduce its float32 dBias among themselves over NCCL
+(N = 8 at H = 4: pairs). The value is whole-problem FLOPs / max-over-ranks device time (total work
+fixed: strong scaling).
 
 Prints ONE JSON line on rank 0 (see the keys below). ``--impl reference`` times the CPU
 restatement of the reference's naive path (oracle/) on the host cores instead, on rank 0 only.
@@ -180,14 +182,25 @@ def main():
     w = workloads.WORKLOADS[WORKLOAD]
     if args.rows > 0:
         w = w.with_rows(min(args.rows, w.L1))
-    rows = fta.shard_rows(w.L1, rank, world)
+    # heads first (no exchange between ranks that own different heads), L1 rows second (ranks that
+    # share a head all-reduce its float32 dBias among themselves)
+    heads, rows, peers = fta.shard_plan(w.H, w.L1, rank, world)
     nrows = rows.stop - rows.start
     dt = torch.bfloat16
     x = workloads.make_inputs(w, rows)
-    host = {k: torch.from_numpy(x[k]).to(dt).pin_memory() for k in ("q", "k", "v", "do", "bias")}
+    host = {k: torch.from_numpy(np.ascontiguousarray(x[k][:, heads])).to(dt).pin_memory()
+            for k in ("q", "k", "v", "do", "bias")}
     d = {k: v.to(dev) for k, v in host.items()}
     L = _cabi.lib()
-    B, H, L2, D = w.B, w.H, w.L2, w.D
+    B, H, L2, D = w.B, heads.stop - heads.start, w.L2, w.D  # H: heads of this rank
+    row_shards = len(peers)
+    grp = None
+    if world > 1 and row_shards > 1:
+        # every rank takes part in the creation of every subgroup
+        for g0 in range(0, world, row_shards):
+            g_ = dist.new_group(list(range(g0, g0 + row_shards)))
+            if g0 == peers[0]:
+                grp = g_
     prob = FtaProblem(B, H, nrows, L2, D, _cabi.FTA_BF16)
     o = torch.empty_like(d["q"])
     lse = torch.empty(3, B, H, nrows, L2, dtype=torch.float32, device=dev)
@@ -201,7 +214,7 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
     stream = torch.cuda.current_stream().cuda_stream
     scale = w.sm_scale
-    sharded = world > 1
+    sharded = grp is not None
 
     def step():
         _cabi.check(L.fta_forward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), scale, t5(o),
@@ -212,7 +225,7 @@ def main():
                                    db32.data_ptr(), None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
                                    status.data_ptr(), stream), "fta_backward")
         if sharded:
-            dist.all_reduce(db32)
+            dist.all_reduce(db32, group=grp)
             _cabi.check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
                         "fta_dbias_cast")
 
@@ -252,7 +265,7 @@ def main():
                                    db32.data_ptr(), None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
                                    status.data_ptr(), stream), "fta_backward")
         if sharded:
-            dist.all_reduce(db32)
+            dist.all_reduce(db32, group=grp)
             _cabi.check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
                         "fta_dbias_cast")
         e1.record()
@@ -282,7 +295,6 @@ def main():
     db_host = torch.empty_like(host["bias"]).pin_memory()
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = sum(v.numel() * v.element_size() for v in out_host.values()) + db_host.numel() * db_host.element_size()
-    grp = dist.group.WORLD if sharded else None
 
     out_host["dbias"] = db_host
 
@@ -320,8 +332,10 @@ def main():
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD if args.rows <= 0 else f"{WORKLOAD}[first {w.L1} rows]", "B": B, "H": H, "L1": w.L1, "L2": L2, "D": D,
-                       "rows_per_gpu": nrows, "parallelism": f"L1 rows sharded over {world} GPU(s)",
+            "config": {"workload": WORKLOAD if args.rows <= 0 else f"{WORKLOAD}[first {w.L1} rows]", "B": B, "H": w.H,
+                       "L1": w.L1, "L2": L2, "D": D, "heads_per_gpu": H, "rows_per_gpu": nrows,
+                       "parallelism": (f"{world // row_shards} head shard(s) x {row_shards} L1-row shard(s); "
+                                       f"dBias all-reduce among {row_shards} rank(s)"),
                        "l2": "flushed between steps (256 MB write outside the events)",
                        "fwd_ms": float(np.mean(fwd_ms)), "bwd_kernel_ms": bwd_kernel_ms,
                        "frac_of_bf16_peak": value / (peak_tf * world), "peak": f"{peak_tf} TFLOP/s {peak_kind}",

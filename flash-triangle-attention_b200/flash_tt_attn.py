@@ -32,7 +32,7 @@ import _cabi
 from _cabi import FtaProblem, check, t4, t5
 
 __all__ = ["attention", "attention_fwd_bwd_streamed", "reference_tt_attn", "check_device_status",
-           "last_dbias_f32"]
+           "last_dbias_f32", "shard_plan", "shard_rows"]
 
 _DEBUG = os.environ.get("FTA_DEBUG", "0") == "1"
 _status_words = {}
@@ -192,6 +192,25 @@ def reference_tt_attn(q, k, v, b, sm_scale):
     logits = torch.einsum("bhijd,bhikd->bhijk", q, k) * sm_scale + b.unsqueeze(2)
     p = torch.softmax(logits.float(), dim=-1).to(v.dtype)
     return torch.einsum("bhijk,bhikd->bhijd", p, v)
+
+
+def shard_plan(H: int, L1: int, rank: int, world: int):
+    """How ``world`` ranks split one triangle-attention problem: heads first, L1 rows second.
+
+    Heads are independent problems INCLUDING their dBias, so ranks that own different heads never
+    exchange anything; only ranks that share a head (they own different blocks of its L1 rows)
+    sum their float32 dBias. ``gcd(world, H)`` head shards, ``world / gcd`` row shards per head
+    shard; ranks of one head shard are consecutive.
+
+    Returns ``(heads, rows, peers)``: this rank's slice of H, its slice of L1, and the ranks it
+    all-reduces dBias with (a list; of length 1 when no collective is needed)."""
+    import math
+    hs = math.gcd(world, H)
+    rs = world // hs
+    hi, ri = rank // rs, rank % rs
+    per_h = H // hs
+    heads = slice(hi * per_h, (hi + 1) * per_h)
+    return heads, shard_rows(L1, ri, rs), list(range(hi * rs, (hi + 1) * rs))
 
 
 def shard_rows(L1: int, rank: int, world: int) -> slice:

@@ -92,3 +92,19 @@ def test_sharded_rows_with_gloo_allreduce(tmp_path):
     outs = [p.communicate(timeout=120)[0] for p in procs]
     for p, out in zip(procs, outs):
         assert p.returncode == 0, out
+
+
+def test_shard_plan_covers_every_head_and_row_once():
+    """Heads first, rows second: every (head, row) belongs to exactly one rank; ranks that share a
+    head are consecutive and form one all-reduce group; different heads never share a group."""
+    import numpy as np
+    for H, L1, world in [(4, 768, 1), (4, 768, 2), (4, 768, 4), (4, 768, 8), (8, 2048, 8), (3, 10, 4), (2, 5, 8)]:
+        cover = np.zeros((H, L1), dtype=np.int32)
+        groups = {}
+        for rank in range(world):
+            heads, rows, peers = fta.shard_plan(H, L1, rank, world)
+            cover[heads, rows] += 1
+            assert rank in peers and peers == list(range(peers[0], peers[0] + len(peers)))
+            groups.setdefault((heads.start, heads.stop), set()).add(tuple(peers))
+        assert (cover == 1).all(), (H, L1, world)
+        assert all(len(g) == 1 for g in groups.values())
