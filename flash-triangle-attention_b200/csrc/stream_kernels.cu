@@ -30,7 +30,9 @@ __device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
 }
 
 // One thread per 8 elements; D/8 adjacent lanes share a row and reduce with shuffles.
-template <int kD, bool kBf16>
+// kDense: both tensors are contiguous, so a row's offset is row * D and the index needs no
+// division (the strided form spends more instructions on 64-bit divisions than on the data).
+template <int kD, bool kBf16, bool kDense>
 __global__ void __launch_bounds__(256) preprocess_kernel(const uint16_t* __restrict__ o,
                                                          const uint16_t* __restrict__ dout,
                                                          float* __restrict__ delta, long long rows,
@@ -47,15 +49,22 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const uint16_t* __restr
     const int part = static_cast<int>(idx % LPR);
     float s = 0.f;
     if (row < rows) {
-      long long r = row;
-      const int j = static_cast<int>(r % L2);
-      r /= L2;
-      const int i = static_cast<int>(r % L1);
-      r /= L1;
-      const int h = static_cast<int>(r % H);
-      const long long b = r / H;
-      const uint4 ov = *reinterpret_cast<const uint4*>(o + b * so_b + h * so_h + i * so_i + j * so_j + part * 8);
-      const uint4 dv = *reinterpret_cast<const uint4*>(dout + b * sd_b + h * sd_h + i * sd_i + j * sd_j + part * 8);
+      long long oo, od;
+      if constexpr (kDense) {
+        oo = od = row * kD + part * 8;
+      } else {
+        long long r = row;
+        const int j = static_cast<int>(r % L2);
+        r /= L2;
+        const int i = static_cast<int>(r % L1);
+        r /= L1;
+        const int h = static_cast<int>(r % H);
+        const long long b = r / H;
+        oo = b * so_b + h * so_h + i * so_i + j * so_j + part * 8;
+        od = b * sd_b + h * sd_h + i * sd_i + j * sd_j + part * 8;
+      }
+      const uint4 ov = __ldg(reinterpret_cast<const uint4*>(o + oo));
+      const uint4 dv = __ldg(reinterpret_cast<const uint4*>(dout + od));
       s = dot8<kBf16>(ov, dv);
     }
 #pragma unroll
@@ -126,7 +135,7 @@ __global__ void __launch_bounds__(256) dbias_finalize_keymajor_kernel(const floa
   }
 }
 
-template <int kD, bool kBf16>
+template <int kD, bool kBf16, bool kDense>
 __global__ void __launch_bounds__(256) dq_finalize_kernel(const float* __restrict__ dq32,
                                                           uint16_t* __restrict__ dq, long long rows,
                                                           int H, int L1, int L2, long long s_b,
@@ -141,19 +150,25 @@ __global__ void __launch_bounds__(256) dq_finalize_kernel(const float* __restric
     const int part = static_cast<int>(idx % LPR);
     const float4 a = __ldg(reinterpret_cast<const float4*>(dq32 + row * kD + part * 8));
     const float4 c = __ldg(reinterpret_cast<const float4*>(dq32 + row * kD + part * 8 + 4));
-    long long r = row;
-    const int j = static_cast<int>(r % L2);
-    r /= L2;
-    const int i = static_cast<int>(r % L1);
-    r /= L1;
-    const int h = static_cast<int>(r % H);
-    const long long b = r / H;
+    long long oo;
+    if constexpr (kDense) {
+      oo = row * kD + part * 8;
+    } else {
+      long long r = row;
+      const int j = static_cast<int>(r % L2);
+      r /= L2;
+      const int i = static_cast<int>(r % L1);
+      r /= L1;
+      const int h = static_cast<int>(r % H);
+      const long long b = r / H;
+      oo = b * s_b + h * s_h + i * s_i + j * s_j + part * 8;
+    }
     uint4 out;
     out.x = pack2<kBf16>(a.x * scale, a.y * scale);
     out.y = pack2<kBf16>(a.z * scale, a.w * scale);
     out.z = pack2<kBf16>(c.x * scale, c.y * scale);
     out.w = pack2<kBf16>(c.z * scale, c.w * scale);
-    *reinterpret_cast<uint4*>(dq + b * s_b + h * s_h + i * s_i + j * s_j + part * 8) = out;
+    *reinterpret_cast<uint4*>(dq + oo) = out;
   }
 }
 
@@ -206,15 +221,25 @@ int launch_preprocess(const void* o, const long long so[4], const void* dout, co
   const int grid = grid_for(rows * (D / 8), 256);
   const uint16_t* op = static_cast<const uint16_t*>(o);
   const uint16_t* dp = static_cast<const uint16_t*>(dout);
-#define FTA_PRE(DD, BF)                                                                          \
-  preprocess_kernel<DD, BF><<<grid, 256, 0, stream>>>(op, dp, delta, rows, H, L1, L2, so[0],      \
-                                                      so[1], so[2], so[3], sdo[0], sdo[1], sdo[2], \
-                                                      sdo[3])
+  auto is_dense = [&](const long long s4[4]) {
+    return s4[3] == D && s4[2] == static_cast<long long>(L2) * D && s4[1] == static_cast<long long>(L1) * L2 * D &&
+           s4[0] == static_cast<long long>(H) * L1 * L2 * D;
+  };
+  const bool dense = is_dense(so) && is_dense(sdo);
+#define FTA_PRE(DD, BF, DN)                                                                          \
+  preprocess_kernel<DD, BF, DN><<<grid, 256, 0, stream>>>(op, dp, delta, rows, H, L1, L2, so[0],      \
+                                                          so[1], so[2], so[3], sdo[0], sdo[1], sdo[2], \
+                                                          sdo[3])
+#define FTA_PRE2(DD, BF) \
+  do {                   \
+    if (dense) FTA_PRE(DD, BF, true); else FTA_PRE(DD, BF, false); \
+  } while (0)
   if (D == 32) {
-    if (bf16) FTA_PRE(32, true); else FTA_PRE(32, false);
+    if (bf16) FTA_PRE2(32, true); else FTA_PRE2(32, false);
   } else {
-    if (bf16) FTA_PRE(64, true); else FTA_PRE(64, false);
+    if (bf16) FTA_PRE2(64, true); else FTA_PRE2(64, false);
   }
+#undef FTA_PRE2
 #undef FTA_PRE
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
@@ -257,14 +282,21 @@ int launch_dq_finalize(const float* dq32, void* dq, const long long sdq[4], int 
   const long long rows = static_cast<long long>(B) * H * L1 * L2;
   const int grid = grid_for(rows * (D / 8), 256);
   uint16_t* out = static_cast<uint16_t*>(dq);
-#define FTA_DQ(DD, BF)                                                                         \
-  dq_finalize_kernel<DD, BF><<<grid, 256, 0, stream>>>(dq32, out, rows, H, L1, L2, sdq[0], sdq[1], \
-                                                       sdq[2], sdq[3], scale)
+  const bool dense = sdq[3] == D && sdq[2] == static_cast<long long>(L2) * D &&
+                     sdq[1] == static_cast<long long>(L1) * L2 * D && sdq[0] == static_cast<long long>(H) * L1 * L2 * D;
+#define FTA_DQ(DD, BF, DN)                                                                              \
+  dq_finalize_kernel<DD, BF, DN><<<grid, 256, 0, stream>>>(dq32, out, rows, H, L1, L2, sdq[0], sdq[1], \
+                                                           sdq[2], sdq[3], scale)
+#define FTA_DQ2(DD, BF) \
+  do {                  \
+    if (dense) FTA_DQ(DD, BF, true); else FTA_DQ(DD, BF, false); \
+  } while (0)
   if (D == 32) {
-    if (bf16) FTA_DQ(32, true); else FTA_DQ(32, false);
+    if (bf16) FTA_DQ2(32, true); else FTA_DQ2(32, false);
   } else {
-    if (bf16) FTA_DQ(64, true); else FTA_DQ(64, false);
+    if (bf16) FTA_DQ2(64, true); else FTA_DQ2(64, false);
   }
+#undef FTA_DQ2
 #undef FTA_DQ
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
