@@ -242,19 +242,22 @@ def main():
 
     # ---- timed region: K steps, each bracketed by CUDA events on the launching stream; L2 is
     # flushed (a 256 MB write) between steps, outside the events. Backward-kernel events too.
-    ev_k0, ev_k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev_k0.record()  # creates the underlying cudaEvent_t handles
-    ev_k1.record()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     step_ms, fwd_ms, bwdk_ms = [], [], []
     barrier()
     wall0 = time.perf_counter()
+    # The host only enqueues: events are recorded on the stream around every step and read after
+    # the loop, so the GPU always has the next launches queued (with a synchronise per step the
+    # host's launch sequence would sit exposed between the short kernels of a multi-GPU shard).
+    evs = []
     for it in range(args.steps):
         flush.zero_()
-        e0, e1, ef = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        L.fta_profile_backward_kernel(ev_k0.cuda_event, ev_k1.cuda_event)
+        e0, e1, ef, k0, k1 = (torch.cuda.Event(enable_timing=True) for _ in range(5))
+        k0.record()  # creates the underlying cudaEvent_t handles (re-recorded inside fta_backward)
+        k1.record()
+        L.fta_profile_backward_kernel(k0.cuda_event, k1.cuda_event)
         e0.record()
         _cabi.check(L.fta_forward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), scale, t5(o),
                                   lse.data_ptr(), status.data_ptr(), stream), "fta_forward")
@@ -269,10 +272,12 @@ def main():
             _cabi.check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
                         "fta_dbias_cast")
         e1.record()
-        torch.cuda.synchronize()
+        evs.append((e0, e1, ef, k0, k1))
+    torch.cuda.synchronize()
+    for e0, e1, ef, k0, k1 in evs:
         step_ms.append(e0.elapsed_time(e1))
         fwd_ms.append(e0.elapsed_time(ef))
-        bwdk_ms.append(ev_k0.elapsed_time(ev_k1))
+        bwdk_ms.append(k0.elapsed_time(k1))
     barrier()
     wall = time.perf_counter() - wall0
     L.fta_profile_backward_kernel(None, None)
