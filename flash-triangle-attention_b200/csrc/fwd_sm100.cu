@@ -404,22 +404,46 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // pass 2: p = 2^((x - m) * log2e), row sum, pack, hand P to the tensor core through TMEM
         const f32x2 nm2 = mk2(-m_safe, -m_safe);
         f32x2 sum2a = mk2(0.f, 0.f), sum2b = mk2(0.f, 0.f);
+        // One fused multiply-add per pair while every row max of the warp is moderate; rows with a
+        // huge |max| (keys masked with -1e9) need (x - m) formed first: it is exact when x is close
+        // to m whatever their magnitude, whereas x*log2e - m*log2e would round m*log2e to the ulp
+        // of 1e9.
+        const bool moderate = __all_sync(0xffffffffu, fabsf(m_safe) <= 1.0e4f);
+        if (moderate) {
+          const float nml = -m_safe * kLog2e;
+          const f32x2 nml2 = mk2(nml, nml);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float y0, y1;
-            // (x - m) first: exact when x is close to m, whatever their magnitude (masked rows)
-            un2(mul2(add2(mk2(__uint_as_float(sr[c * 32 + 2 * j]), __uint_as_float(sr[c * 32 + 2 * j + 1])), nm2),
-                     log2e2),
-                y0, y1);
-            const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-            if (j & 1) sum2b = add2(sum2b, mk2(p0, p1));
-            else sum2a = add2(sum2a, mk2(p0, p1));
-            pk[j] = pack2<kBf16>(p0, p1);
+            for (int j = 0; j < 16; ++j) {
+              float y0, y1;
+              un2(fma2(mk2(__uint_as_float(sr[c * 32 + 2 * j]), __uint_as_float(sr[c * 32 + 2 * j + 1])), log2e2, nml2),
+                  y0, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              if (j & 1) sum2b = add2(sum2b, mk2(p0, p1));
+              else sum2a = add2(sum2a, mk2(p0, p1));
+              pk[j] = pack2<kBf16>(p0, p1);
+            }
+            tmem_st16(tP + c * 16, pk);
           }
-          tmem_st16(tP + c * 16, pk);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float y0, y1;
+              un2(mul2(add2(mk2(__uint_as_float(sr[c * 32 + 2 * j]), __uint_as_float(sr[c * 32 + 2 * j + 1])), nm2),
+                       log2e2),
+                  y0, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              if (j & 1) sum2b = add2(sum2b, mk2(p0, p1));
+              else sum2a = add2(sum2a, mk2(p0, p1));
+              pk[j] = pack2<kBf16>(p0, p1);
+            }
+            tmem_st16(tP + c * 16, pk);
+          }
         }
         float s0, s1;
         un2(add2(sum2a, sum2b), s0, s1);
