@@ -83,6 +83,8 @@ __device__ unsigned long long g_progress[128];
 #ifndef FTA_EXP_P2
 #define FTA_EXP_P2 2
 #endif
+#define FTA_EXP_P1_CONST 2  // compile-time chunk counts; FTA_EXP_P1 / P2 == 0 skips the phase at run time
+#define FTA_EXP_P2_CONST 2
 #ifndef FTA_EXP_DUMP
 #define FTA_EXP_DUMP 4
 #endif
@@ -659,31 +661,34 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const bool robust = __any_sync(0xffffffffu, cq != cq);
           if (!robust) {
             // y = s*scale*log2e + b*log2e + c
-#pragma unroll
-            for (int c16 = 0; c16 < FTA_EXP_P1; ++c16) {
-              uint32_t sv[16];
-              tmem_ld16(tST + c16 * 16, sv);
+            // The 32 columns come in four loads of 8, each issued before the arithmetic on the
+            // previous one and waited for after it, so only the first TMEM round trip is exposed.
+            uint32_t sv[2][8];
+            constexpr int NCH = 2 * FTA_EXP_P1_CONST;
+            if (FTA_EXP_P1 > 0) {
+              tmem_ld8(tST, sv[0]);
               tmem_ld_wait();
+            }
 #pragma unroll
-              for (int c8 = 0; c8 < 2; ++c8) {
-                const int ch = c16 * 2 + c8;  // 8-query chunk within the quarter
-                const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((sub * 4 + ch) ^ (key & 7)) << 4));
-                const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-                const float4 ca = c4[ch * 2], cb = c4[ch * 2 + 1];
-                const f32x2 c2[4] = {mk2(ca.x, ca.y), mk2(ca.z, ca.w), mk2(cb.x, cb.y), mk2(cb.z, cb.w)};
+            for (int ch = 0; ch < NCH; ++ch) {  // 8-query chunk within the quarter
+              if (FTA_EXP_P1 == 0) break;
+              if (ch + 1 < NCH) tmem_ld8(tST + (ch + 1) * 8, sv[(ch + 1) & 1]);
+              const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((sub * 4 + ch) ^ (key & 7)) << 4));
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+              const float4 ca = c4[ch * 2], cb = c4[ch * 2 + 1];
+              const f32x2 c2[4] = {mk2(ca.x, ca.y), mk2(ca.z, ca.w), mk2(cb.x, cb.y), mk2(cb.z, cb.w)};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int idx = c8 * 8 + 2 * e;  // column within the 16-column load
-                  float b0, b1, y0, y1;
-                  unpack2<kBf16>(bw[e], b0, b1);
-                  un2(fma2(mk2(__uint_as_float(sv[idx]), __uint_as_float(sv[idx + 1])), k1_2,
-                           fma2(mk2(b0, b1), log2e2, c2[e])),
-                      y0, y1);
-                  const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-                  pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                  ph[ch * 4 + e] = (kBf16 && FTA_EXP_PH16) ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
-                }
+              for (int e = 0; e < 4; ++e) {
+                float b0, b1, y0, y1;
+                unpack2<kBf16>(bw[e], b0, b1);
+                un2(fma2(mk2(__uint_as_float(sv[ch & 1][2 * e]), __uint_as_float(sv[ch & 1][2 * e + 1])), k1_2,
+                         fma2(mk2(b0, b1), log2e2, c2[e])),
+                    y0, y1);
+                const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+                pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
+                ph[ch * 4 + e] = (kBf16 && FTA_EXP_PH16) ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
               }
+              if (ch + 1 < NCH) tmem_ld_wait();
             }
           } else {
 #pragma unroll
@@ -730,27 +735,31 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_after_sync();
           if ((warp & 3) == 0) FTA_STAMP(qd, 3, tt);
           uint32_t dd[16];  // dS^T of this key row, 32 queries, packed 16-bit pairs
+          {
+            uint32_t dv[2][8];  // four loads of 8 columns, pipelined like phase 1
+            constexpr int NCH = 2 * FTA_EXP_P2_CONST;
+            if (FTA_EXP_P2 > 0) {
+              tmem_ld8(tDP, dv[0]);
+              tmem_ld_wait();
+            }
 #pragma unroll
-          for (int c16 = 0; c16 < FTA_EXP_P2; ++c16) {
-            uint32_t dv[16];
-            tmem_ld16(tDP + c16 * 16, dv);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c8 = 0; c8 < 2; ++c8) {
-              const int ch = c16 * 2 + c8;
+            for (int ch = 0; ch < NCH; ++ch) {
+              if (FTA_EXP_P2 == 0) break;
+              if (ch + 1 < NCH) tmem_ld8(tDP + (ch + 1) * 8, dv[(ch + 1) & 1]);
               const float4 da = del4[ch * 2], db = del4[ch * 2 + 1];
               const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int idx = c8 * 8 + 2 * e;
                 float p0, p1, ds0, ds1;
                 unpack2<(kBf16 && !FTA_EXP_PH16)>(ph[ch * 4 + e], p0, p1);
-                const f32x2 u = fma2(del2[e], neg1_2, mk2(__uint_as_float(dv[idx]), __uint_as_float(dv[idx + 1])));
+                const f32x2 u = fma2(del2[e], neg1_2,
+                                     mk2(__uint_as_float(dv[ch & 1][2 * e]), __uint_as_float(dv[ch & 1][2 * e + 1])));
                 const f32x2 ds = mul2(mk2(p0, p1), u);
                 acc[ch * 4 + e] = add2(acc[ch * 4 + e], ds);
                 un2(ds, ds0, ds1);
                 dd[ch * 4 + e] = pack2<kBf16>(ds0, ds1);
               }
+              if (ch + 1 < NCH) tmem_ld_wait();
             }
           }
           tmem_st16(tDP, dd);
