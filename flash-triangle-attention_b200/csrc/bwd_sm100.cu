@@ -64,17 +64,6 @@ __device__ unsigned long long g_trace_bwd[8192];
 #define FTA_SSTAMP(ev, tile) do { } while (0)
 #endif
 
-#ifdef FTA_PROGRESS
-// Debug build only: each warp notes where it is (code, counter) in shared memory; a CTA that
-// aborts copies the notes and the parity of every barrier to global memory at tear-down.
-__device__ unsigned long long g_progress[128];
-#define FTA_PROG(code, cnt)                                                                  \
-  do {                                                                                       \
-    if ((threadIdx.x & 31) == 0) s_prog[threadIdx.x >> 5] = ((unsigned)(code) << 20) | ((unsigned)(cnt) & 0xfffff); \
-  } while (0)
-#else
-#define FTA_PROG(code, cnt) do { } while (0)
-#endif
 
 // experiment switches (timing studies only; the defaults are the real kernel)
 #ifndef FTA_EXP_P1
@@ -198,9 +187,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #ifdef FTA_TRACE
   unsigned long long* s_trace = reinterpret_cast<unsigned long long*>(abort_flag + 3);
 #endif
-#ifdef FTA_PROGRESS
-  volatile unsigned* s_prog = reinterpret_cast<volatile unsigned*>(abort_flag + 4);
-#endif
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
@@ -215,11 +201,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int row_begin = static_cast<int>(static_cast<long long>(r) * p.L1 / p.NP);
   const int row_end = static_cast<int>(static_cast<long long>(r + 1) * p.L1 / p.NP);
   const int ngroups = (row_end - row_begin + G - 1) / G;
-#ifdef FTA_TRACE
-  const WaitCtx w{smem_u32(abort_flag), p.status, blockIdx.x == 0 ? g_trace_bwd + 15 * 512 : nullptr};
-#else
   const WaitCtx w{smem_u32(abort_flag), p.status};
-#endif
 
 #ifdef FTA_TRACE
   if (threadIdx.x < 256) s_trace[threadIdx.x] = 0;
@@ -280,7 +262,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = row_begin + n * G;
         const int Gc = min(G, row_end - i0);
-        FTA_PROG(0x12, n);
         ok = mbar_wait_warp(bar(C::B_KVFREE), (n & 1) ^ 1, w, 0x21);
         if (!ok) break;
         if (elect_one()) {
@@ -302,7 +283,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
           const int bs = nb & 1;
-          FTA_PROG(0x10, nb);
           ok = mbar_wait_warp(bar(C::B_BIASEMPTY + bs), ((nb >> 1) & 1) ^ 1, w, 0x22);
           if (!ok) break;
           if (elect_one()) {
@@ -315,7 +295,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           for (int g = 0; g < Gc; ++g, ++tt) {
             const int s = tt % C::NQ;
-            FTA_PROG(0x11, tt);
             ok = mbar_wait_warp(bar(C::B_QDOEMPTY + s), ((tt / C::NQ) & 1) ^ 1, w, 0x23);
             if (!ok) break;
             if (elect_one()) {
@@ -378,7 +357,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int i0 = row_begin + n * G;
         const int Gc = min(G, row_end - i0);
         const int T = nq * Gc;
-        FTA_PROG(0x25, n);
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32) &&
              mbar_wait_warp(bar(C::B_QDOFULL + tt % C::NQ), (tt / C::NQ) & 1, w, 0x31);
         if (!ok) break;
@@ -392,12 +370,10 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const bool more = t + 1 < T;
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 1 done: dV, then the next S^T
             if (wh == 0 && lane == 0) FTA_SSTAMP(0, tt);
-            FTA_PROG(0x20 + wh, tt);
             ok = mbar_wait_warp(bar(C::B_P1FULL + wh), tt & 1, w, 0x33);
             if (lane == 0) FTA_SSTAMP(1 + wh, tt);
             if (ok && t == 0 && wh == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
             if (ok && more && wh == 0) {
-              FTA_PROG(0x24, tt);
               ok = mbar_wait_warp(bar(C::B_QDOFULL + (tt + 1) % C::NQ), ((tt + 1) / C::NQ) & 1, w, 0x35);
             }
             if (!ok) break;
@@ -407,7 +383,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 2 done: dK, then the next dP^T
             if (wh == 0 && lane == 0) FTA_SSTAMP(3, tt);
-            FTA_PROG(0x22 + wh, tt);
             ok = mbar_wait_warp(bar(C::B_P2FULL + wh), tt & 1, w, 0x39);
             if (lane == 0) FTA_SSTAMP(4 + wh, tt);
             if (!ok) break;
@@ -444,7 +419,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x36);
         for (int t = 0; t < T && ok; ++t, ++tt) {
           const int g = t % Gc;
-          FTA_PROG(0x30, tt);
           ok = mbar_wait_warp(bar(C::B_P2FULL + 0), tt & 1, w, 0x37) &&
                mbar_wait_warp(bar(C::B_P2FULL + 1), tt & 1, w, 0x38);
           if (!ok) break;
@@ -480,7 +454,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       bool ok = true;
       int k = 0, nb = 0;  // dQ tiles / query blocks so far
       auto dq_event = [&](int irow, int jblk) -> bool {
-        FTA_PROG(0x40, k);
         if (!mbar_wait_warp(bar(C::B_DQSFULL), k & 1, w, 0x51)) return false;
         if (elect_one()) {
           const long long row0 = (static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128;
@@ -508,7 +481,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           const int bs = nb & 1;
           // second warpgroup of each half: boxes parked in the dS tile (needed again soonest)
-          FTA_PROG(0x41, nb);
           ok = mbar_wait_warp(bar(C::B_FLB + 0), nb & 1, w, 0x52) && mbar_wait_warp(bar(C::B_FLB + 1), nb & 1, w, 0x53);
           if (!ok) break;
           if (elect_one()) {
@@ -523,7 +495,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           __syncwarp();
           // first warpgroup of each half: boxes parked in the bias stage
-          FTA_PROG(0x42, nb);
           ok = mbar_wait_warp(bar(C::B_FLA + 0), nb & 1, w, 0x54) && mbar_wait_warp(bar(C::B_FLA + 1), nb & 1, w, 0x55);
           if (!ok) break;
           if (elect_one()) {
@@ -548,11 +519,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           ok = dq_event(i0 + pt % Gc, pt / Gc);
         }
         // the next group adds to the plane elements this group wrote: finish these writes first
-        FTA_PROG(0x45, n);
         if (elect_one()) bulk_wait_all();
         __syncwarp();
       }
-      FTA_PROG(0x46, 0);
       if (elect_one()) bulk_wait_all();
       __syncwarp();
     }
@@ -625,7 +594,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < 16; ++c) acc[c] = mk2(0.f, 0.f);
         const int bs = nb & 1;
-        FTA_PROG(0x54, nb);
         ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
         if (!ok) break;
         if ((warp & 3) == 0) FTA_STAMP(6 + qd, 0, nb);
@@ -640,7 +608,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           }
           const uint8_t* st = sQDO + s * C::STAGE_B;
           if ((warp & 3) == 0) FTA_STAMP(qd, 0, tt);
-          FTA_PROG(0x50, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), ring_par, w, 0x43);  // statistics visible
@@ -729,7 +696,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
           if ((warp & 3) == 0) FTA_STAMP(qd, 2, tt);
           // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
-          FTA_PROG(0x51, tt);
           ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
           if (!ok) break;
           tc_fence_after_sync();
@@ -765,7 +731,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_st16(tDP, dd);
           if ((warp & 3) == 0) FTA_STAMP(qd, 4, tt);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
-            FTA_PROG(0x52, tt);
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
             if (!ok) break;
           }
@@ -812,13 +777,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           // ---- group epilogue, before the dBias boxes so that the dK / dV stores are not queued
           // behind their reductions: last dQ tile, then dK / dV of the G rows
           if ((warp & 3) == 0) FTA_STAMP(10 + qd, 0, n);
-          FTA_PROG(0x55, n);
           ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
           if (!ok) break;
           if ((warp & 3) == 0) FTA_STAMP(10 + qd, 1, n);
           tc_fence_after_sync();
           {
-            FTA_PROG(0x56, tt);
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
             if (!ok) break;
             tc_fence_after_sync();
@@ -866,7 +829,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // their bias values; waiting for their phase-2 arrival rather than the earlier phase-1 one
         // also keeps the two warpgroups of the half in step, which measures faster), the second
         // one that half's part of the dS tile (free once the last dQ MMA has read it).
-        FTA_PROG(0x53, nb);
         if (sub == 0) ok = mbar_wait_warp(bar(C::B_P2FULL + wh), (tt - 1) & 1, w, 0x49);
         else ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x4a);
         if (!ok) break;
@@ -895,21 +857,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) __nanosleep(20000);
-#ifdef FTA_PROGRESS
-  if (*abort_flag) {
-    if (threadIdx.x == 0 && g_progress[127] == 0) atomicCAS(&g_progress[127], 0ull, (unsigned long long)blockIdx.x + 1);
-    __syncthreads();
-    if (g_progress[127] == blockIdx.x + 1) {
-      if (threadIdx.x < 20) g_progress[threadIdx.x] = s_prog[threadIdx.x];
-      if (threadIdx.x < C::NBAR) {
-        uint32_t p0;
-        asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }"
-                     : "=r"(p0) : "r"(bar(threadIdx.x)) : "memory");
-        g_progress[32 + threadIdx.x] = p0;  // 1: current phase index is odd
-      }
-    }
-  }
-#endif
   if (warp == 0) tmem_dealloc(tbase, 512);
 #ifdef FTA_TRACE
   if (blockIdx.x == 0 && threadIdx.x == 0)
@@ -958,11 +905,6 @@ int trace_read_bwd(unsigned long long* host, int n) {
 }
 #endif
 
-#ifdef FTA_PROGRESS
-extern "C" __attribute__((visibility("default"))) int fta_progress_read(unsigned long long* host) {
-  return cudaMemcpyFromSymbol(host, g_progress, sizeof(unsigned long long) * 128) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
 

@@ -137,11 +137,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   // (kept a run-time value: as a compile-time constant it changes the code the compiler generates
   // for the softmax loop, measurably for the worse)
   auto unit_gp = [&](int u) { return unit_i0(u) < p.L1 ? G : 0; };
-#ifdef FTA_TRACE
-  const WaitCtx w{smem_u32(abort_flag), p.status, nullptr};
-#else
   const WaitCtx w{smem_u32(abort_flag), p.status};
-#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;

@@ -93,18 +93,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t pa
 struct WaitCtx {
   uint32_t abort_addr;  // shared-memory address of the CTA's abort word
   int* status;               // global memory, one per launch
-#ifdef FTA_TRACE
-  unsigned long long* dbg;  // debug builds: where each warp of CTA 0 notes the wait it gave up at
-#endif
 };
-#if defined(FTA_TRACE)
-#define FTA_WAIT_NOTE(w, site, parity)                                                        \
-  do {                                                                                        \
-    if ((w).dbg && (threadIdx.x & 31) == 0) (w).dbg[threadIdx.x >> 5] = ((site) << 4) | (parity); \
-  } while (0)
-#else
-#define FTA_WAIT_NOTE(w, site, parity) do { } while (0)
-#endif
+
 
 __device__ __forceinline__ uint32_t ld_shared_volatile_u32(uint32_t addr) {
   uint32_t v;
@@ -136,17 +126,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
 #pragma unroll 1
     for (int j = 0; j < 16; ++j)
       if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
-    if (ld_shared_volatile_u32(w.abort_addr)) {
-      FTA_WAIT_NOTE(w, site, parity);
-      return false;
-    }
+    if (ld_shared_volatile_u32(w.abort_addr)) return false;
     if ((it & 0x3f) == 0x3f) {
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > 1000000000ull) break;
     }
   }
-  FTA_WAIT_NOTE(w, site, parity);
   st_shared_volatile_u32(w.abort_addr, 1u);
   atomicCAS(w.status, kStatusOk, kStatusWaitTimeout | site);
   return false;
