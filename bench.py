@@ -311,7 +311,8 @@ def main():
     if args.no_e2e:
         e2e_steps = 0
     else:
-        e2e_step()
+        for _ in range(3):  # untimed: first touches of the pinned buffers, allocator, streams
+            e2e_step()
     barrier()
     e2e_ms = []
     for _ in range(e2e_steps):

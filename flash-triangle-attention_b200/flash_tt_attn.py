@@ -238,7 +238,25 @@ def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, 
     B, H, L1, L2, D = q_h.shape
     cur = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    nblk = (L1 + block_rows - 1) // block_rows
+    # Block boundaries: full blocks in the middle, a third and two thirds of a block at either end, so
+    # that the first copy in and the last copy out (which nothing overlaps) are short.
+    ramp = [max(1, block_rows // 3), max(1, 2 * block_rows // 3)]
+    sizes = []
+    left = L1
+    if L1 > 3 * block_rows:
+        sizes += ramp
+        left -= 2 * sum(ramp)
+        sizes += [block_rows] * (left // block_rows)
+        if left % block_rows:
+            sizes.append(left % block_rows)
+        sizes += ramp[::-1]
+    else:
+        sizes = [block_rows] * (L1 // block_rows) + ([L1 % block_rows] if L1 % block_rows else [])
+    bounds = [0]
+    for sz in sizes:
+        bounds.append(bounds[-1] + sz)
+    assert bounds[-1] == L1
+    nblk = len(sizes)
     bufs = [{k: torch.empty((B, H, min(block_rows, L1), L2, D), dtype=q_h.dtype, device=dev)
              for k in ("q", "k", "v", "do")} for _ in range(2)]
     ev_in = [torch.cuda.Event() for _ in range(2)]
@@ -257,7 +275,7 @@ def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, 
 
     for blk in range(nblk):
         slot = blk & 1
-        r0, r1 = blk * block_rows, min(L1, (blk + 1) * block_rows)
+        r0, r1 = bounds[blk], bounds[blk + 1]
         with torch.cuda.stream(s_in):
             if blk >= 2:
                 s_in.wait_event(ev_comp[slot])  # the kernels of block blk-2 have read this slot
