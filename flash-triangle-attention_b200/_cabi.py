@@ -59,9 +59,9 @@ def lib():
     L.fta_strerror.argtypes = [ctypes.c_int]
     L.fta_last_cuda_error.restype = ctypes.c_int
     L.fta_forward.restype = ctypes.c_int
-    L.fta_forward.argtypes = [PP, P5, P5, P5, P4, f32, P5, vp, vp, vp]
+    L.fta_forward.argtypes = [PP, P5, P5, P5, P4, f32, P5, vp, vp, vp, vp]
     L.fta_bwd_preprocess.restype = ctypes.c_int
-    L.fta_bwd_preprocess.argtypes = [PP, P5, P5, vp, vp]
+    L.fta_bwd_preprocess.argtypes = [PP, P5, vp, P5, vp, vp]
     L.fta_bwd_workspace_bytes.restype = ctypes.c_size_t
     L.fta_bwd_workspace_bytes.argtypes = [PP]
     L.fta_bwd_num_planes.restype = ctypes.c_int

@@ -14,6 +14,9 @@ int cuda_fail(cudaError_t e) {
   g_last_cuda_error = static_cast<int>(e);
   return FTA_ERR_CUDA;
 }
+int cuda_fail(int e) { return cuda_fail(static_cast<cudaError_t>(e)); }
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 
 int check_problem(const FtaProblem* p) {
   if (!p) return FTA_ERR_NULL;
@@ -74,9 +77,13 @@ int num_sms() {
 
 }  // namespace
 
+namespace fta {
+int record_cuda_error(int cuda_error) { return cuda_fail(cuda_error); }
+}  // namespace fta
+
 extern "C" {
 
-int fta_version(void) { return 100; }
+int fta_version(void) { return 200; }
 
 const char* fta_strerror(int code) {
   switch (code) {
@@ -86,7 +93,7 @@ const char* fta_strerror(int code) {
     case FTA_ERR_HEAD_DIM: return "unsupported head dimension: D must be 32 or 64";
     case FTA_ERR_DTYPE: return "unsupported dtype: fp16 or bf16 only";
     case FTA_ERR_STRIDE: return "bad stride: D stride must be 1, other strides positive multiples of 8 elements";
-    case FTA_ERR_ALIGN: return "base pointer must be 16-byte aligned";
+    case FTA_ERR_ALIGN: return "every device pointer must be 16-byte aligned";
     case FTA_ERR_WORKSPACE: return "workspace too small or misaligned";
     case FTA_ERR_TENSOR_MAP: return "the driver refused a TMA tensor map";
     case FTA_ERR_CUDA: return "a CUDA runtime call failed";
@@ -99,19 +106,21 @@ const char* fta_strerror(int code) {
 int fta_last_cuda_error(void) { return g_last_cuda_error; }
 
 int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k, const FtaTensor5* v,
-                const FtaTensor4* bias, float sm_scale, const FtaTensor5* o, float* lse, int32_t* status,
-                void* stream) {
+                const FtaTensor4* bias, float sm_scale, const FtaTensor5* o, void* o_resid, float* lse,
+                int32_t* status, void* stream) {
   int rc = check_problem(prob);
   if (rc) return rc;
   if ((rc = check_t5(q)) || (rc = check_t5(k)) || (rc = check_t5(v)) || (rc = check_t5(o)) ||
       (rc = check_t4(bias)))
     return rc;
   if (!lse || !status) return FTA_ERR_NULL;
+  if (!aligned16(lse) || !aligned16(o_resid)) return FTA_ERR_ALIGN;
   fta::FwdArgs a;
   if ((rc = map5(&a.tmQ, prob, q)) || (rc = map5(&a.tmK, prob, k)) || (rc = map5(&a.tmV, prob, v)) ||
       (rc = map_bias(&a.tmBias, prob, bias, 64, 128)))
     return rc;
   a.o = o->ptr;
+  a.o_resid = o_resid;
   a.lse = lse;
   a.status = status;
   a.B = prob->B;
@@ -122,24 +131,26 @@ int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k
   a.bf16 = prob->dtype == FTA_BF16;
   for (int i = 0; i < 4; ++i) a.so[i] = o->stride[i];
   a.sm_scale = sm_scale;
-  if (fta::launch_fwd(a, static_cast<cudaStream_t>(stream)) != 0) return cuda_fail(cudaGetLastError());
+  if (const int e = fta::launch_fwd(a, static_cast<cudaStream_t>(stream))) return cuda_fail(e);
   return FTA_OK;
 }
 
-int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const FtaTensor5* dout, float* delta,
-                       void* stream) {
+int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const void* o_resid, const FtaTensor5* dout,
+                       float* delta, void* stream) {
   int rc = check_problem(prob);
   if (rc) return rc;
   if ((rc = check_t5(o)) || (rc = check_t5(dout))) return rc;
   if (!delta) return FTA_ERR_NULL;
+  if (!aligned16(o_resid)) return FTA_ERR_ALIGN;
   long long so[4], sd[4];
   for (int i = 0; i < 4; ++i) {
     so[i] = o->stride[i];
     sd[i] = dout->stride[i];
   }
-  if (fta::launch_preprocess(o->ptr, so, dout->ptr, sd, delta, prob->B, prob->H, prob->L1, prob->L2, prob->D,
-                             prob->dtype == FTA_BF16, static_cast<cudaStream_t>(stream)) != 0)
-    return cuda_fail(cudaGetLastError());
+  if (const int e = fta::launch_preprocess(o->ptr, o_resid, so, dout->ptr, sd, delta, prob->B, prob->H, prob->L1,
+                                           prob->L2, prob->D, prob->dtype == FTA_BF16,
+                                           static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
   return FTA_OK;
 }
 
@@ -167,6 +178,9 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
       (rc = check_t5(dq)) || (rc = check_t5(dk)) || (rc = check_t5(dv)) || (rc = check_t4(bias)))
     return rc;
   if (!lse || !delta || !dbias_f32 || !status || !workspace) return FTA_ERR_NULL;
+  // the kernel fetches the statistics with 512-byte bulk copies and the epilogue writes dBias with
+  // 16-byte stores
+  if (!aligned16(lse) || !aligned16(delta) || !aligned16(dbias_f32) || !aligned16(dbias_cast)) return FTA_ERR_ALIGN;
   if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < fta_bwd_workspace_bytes(prob))
     return FTA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -223,21 +237,17 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
   }
   a.sm_scale = sm_scale;
 
-  cudaError_t e = cudaMemsetAsync(dq32, 0, dq_bytes, st);
-  if (e != cudaSuccess) return cuda_fail(e);
   long long sb[4];
   for (int i = 0; i < 4; ++i) sb[i] = bias->stride[i];
-  if (fta::launch_transpose_bias(bias->ptr, sb, bias_t, prob->B, prob->H, prob->L2, st) != 0)
-    return cuda_fail(cudaGetLastError());
+  if (const int e = fta::launch_bwd_prologue(bias->ptr, sb, bias_t, prob->B, prob->H, prob->L2, dq32,
+                                             static_cast<long long>(rows) * prob->D, st))
+    return cuda_fail(e);
   if (g_prof_start) cudaEventRecord(g_prof_start, st);
-  if (fta::launch_bwd(a, st) != 0) return cuda_fail(cudaGetLastError());
+  if (const int e = fta::launch_bwd(a, st)) return cuda_fail(e);
   if (g_prof_stop) cudaEventRecord(g_prof_stop, st);
-  if (fta::launch_dq_finalize(dq32, dq->ptr, sdq, prob->B, prob->H, prob->L1, prob->L2, prob->D, sm_scale, bf16,
-                              st) != 0)
-    return cuda_fail(cudaGetLastError());
-  if (fta::launch_dbias_finalize_keymajor(planes, nplanes, prob->B * prob->H, prob->L2, dbias_f32, dbias_cast, bf16,
-                                          st) != 0)
-    return cuda_fail(cudaGetLastError());
+  if (const int e = fta::launch_bwd_epilogue(dq32, dq->ptr, sdq, prob->B, prob->H, prob->L1, prob->L2, prob->D,
+                                             sm_scale, planes, nplanes, dbias_f32, dbias_cast, bf16, st))
+    return cuda_fail(e);
   return FTA_OK;
 }
 
@@ -245,9 +255,9 @@ int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* 
   if (!src || !dst) return FTA_ERR_NULL;
   if (n <= 0 || n % 4 != 0) return FTA_ERR_SHAPE;
   if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
-  if (fta::launch_dbias_finalize(src, 1, n, nullptr, dst, dtype == FTA_BF16, static_cast<cudaStream_t>(stream)) !=
-      0)
-    return cuda_fail(cudaGetLastError());
+  if (!aligned16(src) || !aligned16(dst)) return FTA_ERR_ALIGN;
+  if (const int e = fta::launch_dbias_cast(src, n, dst, dtype == FTA_BF16, static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
   return FTA_OK;
 }
 
@@ -268,10 +278,5 @@ int fta_read_status(const int32_t* status, int32_t* code_out, void* stream) {
   if (code_out) *code_out = host;
   return host == 0 ? FTA_OK : FTA_ERR_DEVICE;
 }
-
-#ifdef FTA_TRACE
-FTA_API int fta_trace_read_fwd(unsigned long long* host, int n) { return fta::trace_read_fwd(host, n); }
-FTA_API int fta_trace_read_bwd(unsigned long long* host, int n) { return fta::trace_read_bwd(host, n); }
-#endif
 
 }  // extern "C"

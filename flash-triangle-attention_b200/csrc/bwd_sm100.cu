@@ -44,49 +44,6 @@ constexpr int kBwdThreads = 640;    // 4 service warps + 16 compute warps
 constexpr int kAuxRegs = 56;        // registers per thread of the service warpgroup
 constexpr int kComputeRegs = 104;   // 512 * 104 + 128 * 56 <= 640 * 96, the CTA's register allotment at launch
 
-#ifdef FTA_TRACE
-// Debug build only: clock64() stamps of CTA 0, read back with fta_trace_read_bwd().
-__device__ unsigned long long g_trace_bwd[8192];
-#endif
-#if defined(FTA_TRACE) && !defined(FTA_NOSTAMP)
-#define FTA_STAMP(role, ev, tile)                                                  \
-  do {                                                                             \
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (tile) < 64)                 \
-      g_trace_bwd[((role) * 64 + (tile)) * 8 + (ev)] = clock64();                  \
-  } while (0)
-// same, but kept in shared memory until the end of the kernel (no global store on the way)
-#define FTA_SSTAMP(ev, tile)                                                       \
-  do {                                                                             \
-    if (blockIdx.x == 0 && (tile) < 32) s_trace[(tile) * 8 + (ev)] = clock64();    \
-  } while (0)
-#else
-#define FTA_STAMP(role, ev, tile) do { } while (0)
-#define FTA_SSTAMP(ev, tile) do { } while (0)
-#endif
-
-
-// experiment switches (timing studies only; the defaults are the real kernel)
-#ifndef FTA_EXP_P1
-#define FTA_EXP_P1 2
-#endif
-#ifndef FTA_EXP_P2
-#define FTA_EXP_P2 2
-#endif
-#define FTA_EXP_P1_CONST 2  // compile-time chunk counts; FTA_EXP_P1 / P2 == 0 skips the phase at run time
-#define FTA_EXP_P2_CONST 2
-#ifndef FTA_EXP_DUMP
-#define FTA_EXP_DUMP 4
-#endif
-#ifndef FTA_EXP_PH16
-#define FTA_EXP_PH16 0  // 1: phase 2 reads P from a separate half-precision copy (bf16 inputs)
-#endif
-#ifndef FTA_EXP_DQ_OUT
-#define FTA_EXP_DQ_OUT true
-#endif
-#ifndef FTA_EXP_PLANE_OUT
-#define FTA_EXP_PLANE_OUT true
-#endif
-
 template <int kD>
 struct BwdCfg {
   static constexpr int G = (kD == 32) ? 3 : 1;  // rows per group (TMEM: 256 + 2*D + 2*D*G <= 512)
@@ -127,7 +84,7 @@ struct BwdCfg {
   static constexpr int B_FLB = B_FLA + 2;
   static constexpr int B_DSFREE = B_FLB + 2;  // the two boxes parked in the dS tile have been read
   static constexpr int NBAR = B_DSFREE + 1;
-  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024 + 2048 + 16;  // + trace slots (debug builds)
+  static constexpr int SMEM_BYTES = OFF_BAR + NBAR * 8 + 16 + 1024;  // + tmem slot / abort flag + alignment slack
   static constexpr uint64_t SWZ = (kD == 32) ? kSwz64 : kSwz128;
   static constexpr uint32_t ROW_B = kD * 2;
   static constexpr uint32_t SBO = 8 * ROW_B;
@@ -184,9 +141,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NBAR);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
-#ifdef FTA_TRACE
-  unsigned long long* s_trace = reinterpret_cast<unsigned long long*>(abort_flag + 3);
-#endif
   const uint32_t bar0 = smem_u32(bars);
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
@@ -203,9 +157,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int ngroups = (row_end - row_begin + G - 1) / G;
   const WaitCtx w{smem_u32(abort_flag), p.status};
 
-#ifdef FTA_TRACE
-  if (threadIdx.x < 256) s_trace[threadIdx.x] = 0;
-#endif
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar(C::B_KVFULL), 1);
@@ -369,9 +320,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int jb = t / Gc, g = t % Gc, gn = (t + 1) % Gc;
           const bool more = t + 1 < T;
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 1 done: dV, then the next S^T
-            if (wh == 0 && lane == 0) FTA_SSTAMP(0, tt);
             ok = mbar_wait_warp(bar(C::B_P1FULL + wh), tt & 1, w, 0x33);
-            if (lane == 0) FTA_SSTAMP(1 + wh, tt);
             if (ok && t == 0 && wh == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
             if (ok && more && wh == 0) {
               ok = mbar_wait_warp(bar(C::B_QDOFULL + (tt + 1) % C::NQ), ((tt + 1) / C::NQ) & 1, w, 0x35);
@@ -382,9 +331,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (more) issue_half(0, tt + 1, gn, wh);
           }
           for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 2 done: dK, then the next dP^T
-            if (wh == 0 && lane == 0) FTA_SSTAMP(3, tt);
             ok = mbar_wait_warp(bar(C::B_P2FULL + wh), tt & 1, w, 0x39);
-            if (lane == 0) FTA_SSTAMP(4 + wh, tt);
             if (!ok) break;
             tc_fence_after_sync();
             issue_acc(1, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
@@ -393,7 +340,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               __syncwarp();
             }
             if (more) issue_half(1, tt + 1, gn, wh);
-            if (wh == 1 && lane == 0) FTA_SSTAMP(6, tt);
           }
         }
         if (ok) {
@@ -457,7 +403,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (!mbar_wait_warp(bar(C::B_DQSFULL), k & 1, w, 0x51)) return false;
         if (elect_one()) {
           const long long row0 = (static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128;
-          if (FTA_EXP_DQ_OUT) tma_reduce_add_2d(&tmDQ, smem_u32(sDQ), 0, static_cast<int>(row0));
+          tma_reduce_add_2d(&tmDQ, smem_u32(sDQ), 0, static_cast<int>(row0));
           bulk_commit_group();
           bulk_wait_read_all();  // the staging tile has been read: the compute warps may refill it
           mbar_arrive(bar(C::B_DQSFREE));
@@ -487,7 +433,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int hh = 0; hh < 2; ++hh) {
               const uint32_t src = smem_u32(sDS + hh * 16384);
               const int qcol = jb * 128 + (2 * hh + 1) * 32;
-              if (!(FTA_EXP_PLANE_OUT)) continue;
               if (n == 0) tma_store_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
               else tma_reduce_add_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
             }
@@ -501,7 +446,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int hh = 0; hh < 2; ++hh) {
               const uint32_t src = smem_u32(sBias + bs * C::BIAS_B + hh * 16384);
               const int qcol = jb * 128 + (2 * hh) * 32;
-              if (!(FTA_EXP_PLANE_OUT)) continue;
               if (n == 0) tma_store_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
               else tma_reduce_add_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
             }
@@ -596,7 +540,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const int bs = nb & 1;
         ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nb >> 1) & 1, w, 0x41);
         if (!ok) break;
-        if ((warp & 3) == 0) FTA_STAMP(6 + qd, 0, nb);
         const uint8_t* brow = sBias + bs * C::BIAS_B + wh * 16384 + key * 128;
         for (int g = 0; g < Gc; ++g, ++tt) {
           // Q/dO ring slot and phase of tile tt (tt % NQ, (tt / NQ) & 1) kept as running counters
@@ -607,20 +550,20 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ring_phase ^= 1u;
           }
           const uint8_t* st = sQDO + s * C::STAGE_B;
-          if ((warp & 3) == 0) FTA_STAMP(qd, 0, tt);
           ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
           if (!ok) break;
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), ring_par, w, 0x43);  // statistics visible
           if (!ok) break;
-          if ((warp & 3) == 0) FTA_STAMP(qd, 1, tt);
           tc_fence_after_sync();
           const float4* nm4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B) + qd * 8;
           const float4* nl4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 512) + qd * 8;
           const float4* del4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1024) + qd * 8;
-          // ---- phase 1: P^T = exp2((S^T*scale + bias^T - max)*log2e - log2 sum), handed to the dV MMA.
-          // Phase 2 re-reads P from the packed 16-bit values that also feed the dV MMA (the same
-          // rounded P in dV and dS; a separate fp16 copy for bf16 inputs - FTA_EXP_PH16 - costs 16
-          // registers and 16 conversions per thread and tile for rel-L2 0.0027 instead of 0.0030).
+          // ---- phase 1: P^T = exp2((S^T*scale + bias^T - max)*log2e - log2 sum), handed to the dV MMA
+          // in the input dtype (pp). Phase 2 forms dS from a half-precision (fp16) copy of P (ph):
+          // with bf16 inputs the 8-bit mantissa of the MMA operand would put a rounding error of
+          // up to 2^-9 * |dP - delta| into every term of the dBias sums over L1 (0.04 max-abs at
+          // 768 rows of N(0,1) inputs, twice the tolerance); fp16 keeps 11 bits for 16 conversions
+          // per thread and tile.
           uint32_t ph[16], pp[16];
           const float4* c4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1536) + qd * 8;
           // one lane per query of the quarter looks at c: NaN = a row that needs the two-part form
@@ -631,14 +574,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // The 32 columns come in four loads of 8, each issued before the arithmetic on the
             // previous one and waited for after it, so only the first TMEM round trip is exposed.
             uint32_t sv[2][8];
-            constexpr int NCH = 2 * FTA_EXP_P1_CONST;
-            if (FTA_EXP_P1 > 0) {
-              tmem_ld8(tST, sv[0]);
-              tmem_ld_wait();
-            }
+            constexpr int NCH = 4;
+            tmem_ld8(tST, sv[0]);
+            tmem_ld_wait();
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) {  // 8-query chunk within the quarter
-              if (FTA_EXP_P1 == 0) break;
               if (ch + 1 < NCH) tmem_ld8(tST + (ch + 1) * 8, sv[(ch + 1) & 1]);
               const uint4 bv = *reinterpret_cast<const uint4*>(brow + (((sub * 4 + ch) ^ (key & 7)) << 4));
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -653,7 +593,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
                 pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                ph[ch * 4 + e] = (kBf16 && FTA_EXP_PH16) ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
               }
               if (ch + 1 < NCH) tmem_ld_wait();
             }
@@ -684,7 +624,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 un2(fma2(add2(x, nm2[e]), log2e2, nl2[e]), y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
                 pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                ph[ch * 4 + e] = (kBf16 && FTA_EXP_PH16) ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
               }
             }
           }
@@ -694,30 +634,25 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
-          if ((warp & 3) == 0) FTA_STAMP(qd, 2, tt);
           // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
           ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
           if (!ok) break;
           tc_fence_after_sync();
-          if ((warp & 3) == 0) FTA_STAMP(qd, 3, tt);
           uint32_t dd[16];  // dS^T of this key row, 32 queries, packed 16-bit pairs
           {
             uint32_t dv[2][8];  // four loads of 8 columns, pipelined like phase 1
-            constexpr int NCH = 2 * FTA_EXP_P2_CONST;
-            if (FTA_EXP_P2 > 0) {
-              tmem_ld8(tDP, dv[0]);
-              tmem_ld_wait();
-            }
+            constexpr int NCH = 4;
+            tmem_ld8(tDP, dv[0]);
+            tmem_ld_wait();
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) {
-              if (FTA_EXP_P2 == 0) break;
               if (ch + 1 < NCH) tmem_ld8(tDP + (ch + 1) * 8, dv[(ch + 1) & 1]);
               const float4 da = del4[ch * 2], db = del4[ch * 2 + 1];
               const f32x2 del2[4] = {mk2(da.x, da.y), mk2(da.z, da.w), mk2(db.x, db.y), mk2(db.z, db.w)};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 float p0, p1, ds0, ds1;
-                unpack2<(kBf16 && !FTA_EXP_PH16)>(ph[ch * 4 + e], p0, p1);
+                unpack2<false>(ph[ch * 4 + e], p0, p1);
                 const f32x2 u = fma2(del2[e], neg1_2,
                                      mk2(__uint_as_float(dv[ch & 1][2 * e]), __uint_as_float(dv[ch & 1][2 * e + 1])));
                 const f32x2 ds = mul2(mk2(p0, p1), u);
@@ -729,7 +664,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
           }
           tmem_st16(tDP, dd);
-          if ((warp & 3) == 0) FTA_STAMP(qd, 4, tt);
           if (tt > 0) {  // dS staging tile free again: the previous dQ MMA has read it
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x44);
             if (!ok) break;
@@ -747,10 +681,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, false);
             if (!ok) break;
           }
-          if ((warp & 3) == 0) FTA_STAMP(qd, 5, tt);
           // dS^T row of this key into the M-major staging tile (128-byte swizzle)
 #pragma unroll
-          for (int j = 0; j < FTA_EXP_DUMP; ++j) {
+          for (int j = 0; j < 4; ++j) {
             const uint4 v4 = make_uint4(dd[4 * j], dd[4 * j + 1], dd[4 * j + 2], dd[4 * j + 3]);
             *reinterpret_cast<uint4*>(sDS + wh * 16384 + key * 128 + (((sub * 4 + j) ^ (key & 7)) << 4)) = v4;
           }
@@ -762,7 +695,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_arrive(bar(C::B_P2FULL + wh));
             if (stage_dq) mbar_arrive(bar(C::B_DQSFULL));
           }
-          if ((warp & 3) == 0) FTA_STAMP(qd, 6, tt);
           if (!C::DQ_TMA && !(jb == 0 && g == 0)) {
             // dQ of the previous tile of this group is complete (DQDONE waited above)
             const int pt = jb * Gc + g - 1;
@@ -770,16 +702,13 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, true);
             if (!ok) break;
           }
-          if ((warp & 3) == 0) FTA_STAMP(qd, 7, tt);
         }
         if (!ok) break;
         if (jb == nq - 1) {
           // ---- group epilogue, before the dBias boxes so that the dK / dV stores are not queued
           // behind their reductions: last dQ tile, then dK / dV of the G rows
-          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 0, n);
           ok = mbar_wait_warp(bar(C::B_ACCFULL), n & 1, w, 0x45);
           if (!ok) break;
-          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 1, n);
           tc_fence_after_sync();
           {
             ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x46);  // last dQ of the group
@@ -789,7 +718,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ok = reduce_dq((tt - 1) & 1, i0 + pt % Gc, pt / Gc, true);
             if (!ok) break;
           }
-          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 2, n);
           {
             // half 0 stores dV, half 1 stores dK (scaled by sm_scale, flash_tt_attn.py:518); the two
             // warpgroups of a half take alternate rows of the group
@@ -820,7 +748,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_ACCFREE));
-          if ((warp & 3) == 0) FTA_STAMP(10 + qd, 3, n);
         }
         if (!ok) break;
         // ---- dBias of this query block: the sums go to the store warp as 16 KB boxes parked in
@@ -847,7 +774,6 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) mbar_arrive(bar((sub == 0 ? C::B_FLA : C::B_FLB) + wh));
         }
-        if ((warp & 3) == 0) FTA_STAMP(6 + qd, 1, nb);
       }
       if (!ok) break;
     }
@@ -858,22 +784,14 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   __syncthreads();
   if (*abort_flag) __nanosleep(20000);
   if (warp == 0) tmem_dealloc(tbase, 512);
-#ifdef FTA_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0)
-    for (int i = 0; i < 256; ++i) g_trace_bwd[5 * 512 + i] = s_trace[i];
-#endif
 }
 
 template <int kD, bool kBf16>
 int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   using C = BwdCfg<kD>;
-  static bool attr_set = false;
+  static PerDeviceOnce smem_attr;
   auto kern = fta_bwd_kernel<kD, kBf16>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return -1;
-    attr_set = true;
-  }
+  if (cudaError_t e = ensure_dynamic_smem(smem_attr, kern, C::SMEM_BYTES)) return static_cast<int>(e);
   BwdParams p;
   p.lse = a.lse;
   p.delta = a.delta;
@@ -894,17 +812,10 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
   p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
   const int grid = a.B * a.H * NP * (a.L2 / 128);
   kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, a.tmDQ, a.tmPlane, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace
-
-#ifdef FTA_TRACE
-int trace_read_bwd(unsigned long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, g_trace_bwd, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
-}
-#endif
-
 
 int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
 

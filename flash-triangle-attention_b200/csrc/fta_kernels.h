@@ -5,16 +5,45 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace fta {
+
+// Records `cuda_error` (a cudaError_t) as the calling thread's last CUDA error, the value
+// fta_last_cuda_error() reports; returns FTA_ERR_CUDA.
+int record_cuda_error(int cuda_error);
+
+// Every launch_* function below returns cudaSuccess (0) or the cudaError_t of the call that failed
+// (the launch itself or an attribute call before it); it leaves no sticky error behind.
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a property of a kernel ON ONE DEVICE: a process
+// that drives several GPUs has to set it once per device. One flag per device ordinal; two threads
+// that race on the same device both make the (idempotent) call.
+struct PerDeviceOnce {
+  static constexpr int kMaxDevices = 64;
+  std::atomic<unsigned char> done[kMaxDevices] = {};
+};
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(PerDeviceOnce& once, Kernel kern, int bytes) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const bool tracked = dev >= 0 && dev < PerDeviceOnce::kMaxDevices;
+  if (tracked && once.done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked) once.done[dev].store(1, std::memory_order_release);
+  return e;
+}
 
 struct FwdArgs {
   CUtensorMap tmQ, tmK, tmV, tmBias;
   void* o;
+  void* o_resid;  // nullptr, or the rounding residual of O with O's strides
   float* lse;
   int* status;
   int B, H, L1, L2, D;
   bool bf16;
-  long long so[4];  // element strides of O over (B, H, L1, L2)
+  long long so[4];  // element strides of O (and of the residual) over (B, H, L1, L2)
   float sm_scale;
 };
 int launch_fwd(const FwdArgs& a, cudaStream_t stream);
@@ -39,32 +68,24 @@ int launch_bwd(const BwdArgs& a, cudaStream_t stream);
 int bwd_rows_per_cta(int D);
 int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms);
 
-// delta[row] = sum_d O[row,d] * dO[row,d]
-int launch_preprocess(const void* o, const long long so[4], const void* dout, const long long sdo[4],
-                      float* delta, int B, int H, int L1, int L2, int D, bool bf16,
+// delta[row] = sum_d (O[row,d] + R[row,d]) * dO[row,d]; `o_resid` (R, strides of O) may be nullptr
+int launch_preprocess(const void* o, const void* o_resid, const long long so[4], const void* dout,
+                      const long long sdo[4], float* delta, int B, int H, int L1, int L2, int D, bool bf16,
                       cudaStream_t stream);
 
-// out[bh][k][q] = bias[b][h][q][k] (16-bit elements); `sb` = element strides of the bias
-int launch_transpose_bias(const void* bias, const long long sb[4], void* out, int B, int H, int L2,
-                          cudaStream_t stream);
+// Backward prologue, one launch: bias_t[bh][k][q] = bias[b][h][q][k] (16-bit elements; `sb` = element
+// strides of the bias) and zero-fill of the float32 dQ accumulator (`dq_elems` floats, a multiple of 4)
+int launch_bwd_prologue(const void* bias, const long long sb[4], void* bias_t, int B, int H, int L2, float* dq32,
+                        long long dq_elems, cudaStream_t stream);
 
-// out_f32[e] = sum_p planes[p][e] (fixed order), optional rounded copy
-int launch_dbias_finalize(const float* planes, int nplanes, long long plane_elems, float* out_f32,
-                          void* out_cast, bool bf16, cudaStream_t stream);
+// Backward epilogue, one launch: dq[row, d] = (dtype)(scale * dq32[row, d]) and, for the KEY-MAJOR
+// planes the backward kernel writes, (nplanes, B*H, key, query):
+// dbias_f32[bh][query][key] = sum_p planes[p][bh][key][query] in plane order, optional rounded copy
+int launch_bwd_epilogue(const float* dq32, void* dq, const long long sdq[4], int B, int H, int L1, int L2, int D,
+                        float scale, const float* planes, int nplanes, float* dbias_f32, void* dbias_cast, bool bf16,
+                        cudaStream_t stream);
 
-// The same for the KEY-MAJOR planes the backward kernel writes, (nplanes, B*H, key, query):
-// out[bh][query][key] = sum_p planes[p][bh][key][query] in plane order, optional rounded copy
-int launch_dbias_finalize_keymajor(const float* planes, int nplanes, int BH, int L2, float* out_f32,
-                                   void* out_cast, bool bf16, cudaStream_t stream);
-
-// dq[row, d] = (dtype)(scale * dq32[row, d])
-int launch_dq_finalize(const float* dq32, void* dq, const long long sdq[4], int B, int H, int L1,
-                       int L2, int D, float scale, bool bf16, cudaStream_t stream);
-
-#ifdef FTA_TRACE
-// debug builds only: clock stamps of CTA 0 of the last launch
-int trace_read_fwd(unsigned long long* host, int n);
-int trace_read_bwd(unsigned long long* host, int n);
-#endif
+// dst[i] = (dtype) src[i], n a multiple of 4
+int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaStream_t stream);
 
 }  // namespace fta

@@ -37,18 +37,6 @@ namespace {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLazyThreshold = 5.545177444f;  // 8 / log2(e): rescale when the max grew by > 2^8
 
-#ifdef FTA_TRACE
-// Debug build only: clock64() stamps of CTA (0,0,0), read back with fta_trace_read_fwd().
-__device__ unsigned long long g_trace[8192];
-#define FTA_STAMP(role, ev, tile)                                                          \
-  do {                                                                                     \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 && (tile) < 64) \
-      g_trace[((role) * 64 + (tile)) * 8 + (ev)] = clock64();                              \
-  } while (0)
-#else
-#define FTA_STAMP(role, ev, tile) do { } while (0)
-#endif
-
 template <int kD>
 struct FwdCfg {
   static constexpr int G = (kD == 32) ? 4 : 2;       // rows per CTA (even)
@@ -81,6 +69,7 @@ struct FwdCfg {
 
 struct FwdParams {
   void* o;
+  void* o_resid;  // optional: the part of O lost in rounding to 16 bits, same layout as O
   float* lse;
   int* status;
   int H, L1, L2;
@@ -272,10 +261,8 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!ok) break;
           it_next(ahead);
         }
-        FTA_STAMP(2, 0, cur.tt);
         ok = mbar_wait_warp(bar(C::B_PFULL + wb), npv[wb] & 1, w, 5);
         if (!ok) break;
-        FTA_STAMP(2, 1, cur.tt);
         tc_fence_after_sync();
         const uint64_t dv = umma_smem_desc(sKV_a + s * 2 * C::TILE_B + C::TILE_B, C::SBO, C::SBO, C::SWZ);
         const uint32_t acc0 = cur.kb > 0 ? 1u : 0u;
@@ -288,7 +275,6 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           umma_commit(bar(C::B_PVDONE + wb));
         }
         __syncwarp();
-        FTA_STAMP(2, 2, cur.tt);
         ++npv[wb];
         it_next(cur);
       }
@@ -319,14 +305,12 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const uint8_t* brow = sBias + bs * C::BIAS_B + row * 128;
       for (int gi = 0; gi < ngi; ++gi, ++n) {
         const int g = 2 * gi + wg;
-        if ((warp & 3) == 0) FTA_STAMP(wg, 0, n);
         ok = mbar_wait_warp(bar(C::B_SFULL + wg), n & 1, w, 6);
         if (!ok) break;
         if (gi == 0) {
           ok = mbar_wait_warp(bar(C::B_BIASFULL + bs), (nbias >> 1) & 1, w, 7);
           if (!ok) break;
         }
-        if ((warp & 3) == 0) FTA_STAMP(wg, 1, n);
         tc_fence_after_sync();
         uint32_t sr[128];
 #pragma unroll
@@ -336,7 +320,6 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_SFREE + wg));
-        if ((warp & 3) == 0) FTA_STAMP(wg, 2, n);
         // pass 1: x = s*scale + bias (natural-log units), row max
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -364,7 +347,6 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(C::B_BIASEMPTY + bs));
         }
-        if ((warp & 3) == 0) FTA_STAMP(wg, 3, n);
         const float m_old = sel(m_used, gi);
         const float l_old = sel(l_run, gi);
         const bool need = mx > m_old + kLazyThreshold;
@@ -396,7 +378,6 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           ok = mbar_wait_warp(bar(C::B_PVDONE + wg), (n - 1) & 1, w, 10);
           if (!ok) break;
         }
-        if ((warp & 3) == 0) FTA_STAMP(wg, 4, n);
         // pass 2: p = 2^((x - m) * log2e), row sum, pack, hand P to the tensor core through TMEM
         const f32x2 nm2 = mk2(-m_safe, -m_safe);
         f32x2 sum2a = mk2(0.f, 0.f), sum2b = mk2(0.f, 0.f);
@@ -443,12 +424,10 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         float s0, s1;
         un2(add2(sum2a, sum2b), s0, s1);
-        if ((warp & 3) == 0) FTA_STAMP(wg, 5, n);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::B_PFULL + wg));
-        if ((warp & 3) == 0) FTA_STAMP(wg, 6, n);
         const float l_new = l_old * alpha + (s0 + s1);
         put(m_used, gi, m_new);
         put(l_run, gi, l_new);
@@ -462,8 +441,12 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           const int i = i0 + g;
           const float inv = 1.0f / l_new;
           const int j = jb * 128 + row;
-          uint16_t* optr = reinterpret_cast<uint16_t*>(p.o) + b * p.so_b + h * p.so_h +
-                           static_cast<long long>(i) * p.so_i + static_cast<long long>(j) * p.so_j;
+          const long long ooff = b * p.so_b + h * p.so_h + static_cast<long long>(i) * p.so_i +
+                                 static_cast<long long>(j) * p.so_j;
+          uint16_t* optr = reinterpret_cast<uint16_t*>(p.o) + ooff;
+          // O - dtype(O), rounded to the same dtype: with it the backward preprocess forms
+          // delta = rowsum(dO * O) from O to 16 mantissa bits instead of 8 (bf16)
+          uint16_t* rptr = p.o_resid ? reinterpret_cast<uint16_t*>(p.o_resid) + ooff : nullptr;
 #pragma unroll
           for (int c = 0; c < kD / 32; ++c) {
             uint32_t orr[32];
@@ -478,6 +461,18 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 ov.z = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 4]) * inv, __uint_as_float(orr[v4 * 8 + 5]) * inv);
                 ov.w = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 6]) * inv, __uint_as_float(orr[v4 * 8 + 7]) * inv);
                 *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
+                if (rptr) {
+                  const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+                  uint32_t rw[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    float r0, r1;
+                    unpack2<kBf16>(ow[e], r0, r1);
+                    rw[e] = pack2<kBf16>(__uint_as_float(orr[v4 * 8 + 2 * e]) * inv - r0,
+                                         __uint_as_float(orr[v4 * 8 + 2 * e + 1]) * inv - r1);
+                  }
+                  *reinterpret_cast<uint4*>(rptr + c * 32 + v4 * 8) = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+                }
               }
             }
           }
@@ -510,16 +505,12 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 template <int kD, bool kBf16>
 int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   using C = FwdCfg<kD>;
-  static bool attr_set = false;
+  static PerDeviceOnce smem_attr;
   auto kern = fta_fwd_kernel<kD, kBf16>;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) !=
-        cudaSuccess)
-      return -1;
-    attr_set = true;
-  }
+  if (cudaError_t e = ensure_dynamic_smem(smem_attr, kern, C::SMEM_BYTES)) return static_cast<int>(e);
   FwdParams p;
   p.o = a.o;
+  p.o_resid = a.o_resid;
   p.lse = a.lse;
   p.status = a.status;
   p.H = a.H;
@@ -567,7 +558,7 @@ int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   }
   dim3 grid(a.L2 / 128, best_gy, a.B * a.H);
   kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmBias, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace
@@ -576,12 +567,6 @@ int launch_fwd(const FwdArgs& a, cudaStream_t stream) {
   if (a.D == 32) return a.bf16 ? launch_fwd_t<32, true>(a, stream) : launch_fwd_t<32, false>(a, stream);
   return a.bf16 ? launch_fwd_t<64, true>(a, stream) : launch_fwd_t<64, false>(a, stream);
 }
-
-#ifdef FTA_TRACE
-int trace_read_fwd(unsigned long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int fwd_rows_per_cta(int D) { return D == 32 ? FwdCfg<32>::G : FwdCfg<64>::G; }
 

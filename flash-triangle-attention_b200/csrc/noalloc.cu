@@ -12,6 +12,8 @@
 // and that pointer is what the kernels receive.
 #include "../../include/fta.h"
 
+#include "fta_kernels.h"
+
 #include <cuda_runtime.h>
 #include <mutex>
 
@@ -28,12 +30,15 @@ std::mutex g_scratch_mu;
 // Device address of the scratch array on the current device; looked up on first use.
 int scratch_for_current_device(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FTA_ERR_CUDA;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fta::record_cuda_error(e);
+  if (dev < 0 || dev >= kMaxDevices) return fta::record_cuda_error(cudaErrorInvalidDevice);
   std::lock_guard<std::mutex> lock(g_scratch_mu);
   if (!g_scratch_ptr[dev]) {
     void* p = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-    if (e != cudaSuccess || !p) return FTA_ERR_CUDA;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return fta::record_cuda_error(e);
+    if (!p) return fta::record_cuda_error(cudaErrorInvalidSymbol);
     g_scratch_ptr[dev] = p;
   }
   *out = g_scratch_ptr[dev];

@@ -92,7 +92,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t pa
 // Shared abort flag + global status word, carried by every role.
 struct WaitCtx {
   uint32_t abort_addr;  // shared-memory address of the CTA's abort word
-  int* status;               // global memory, one per launch
+  int* status;          // global memory, one per launch
+  unsigned long long limit_ns = 1000000000ull;  // a wait gives up after this long (about a second)
 };
 
 
@@ -117,20 +118,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   // fast path
   if (mbar_try_wait(bar, parity)) return true;
   // Spin on try_wait (which itself suspends the thread for a short, bounded time). The wait
-  // gives up after about a second of wall-clock time, measured with the global nanosecond timer.
+  // gives up after `w.limit_ns` of wall-clock time, measured with the global nanosecond timer.
   // The inner loop is nothing but the poll, so that a waiting warp takes as few issue slots as
-  // possible from the warps that share its scheduler; abort flag and clock are looked at once
-  // per 16 polls.
+  // possible from the warps that share its scheduler; the abort flag is looked at once per
+  // 16 polls, the clock once per 64.
   unsigned long long t0 = 0;
   for (uint32_t it = 0; it < (1u << 26); ++it) {
 #pragma unroll 1
     for (int j = 0; j < 16; ++j)
       if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
     if (ld_shared_volatile_u32(w.abort_addr)) return false;
-    if ((it & 0x3f) == 0x3f) {
+    if ((it & 0x3) == 0x3) {
       const unsigned long long now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 1000000000ull) break;
+      else if (now - t0 > w.limit_ns) break;
     }
   }
   st_shared_volatile_u32(w.abort_addr, 1u);
@@ -451,13 +452,9 @@ __device__ __forceinline__ void reg_dec() {
 // small numeric helpers
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ float fast_exp2(float x) {
-#ifdef FTA_EXP_NOEX2
-  return x * 0.5f;  // timing study only
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -466,51 +463,14 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-// Two fp32 lanes handled together. Packed build: one 64-bit register, Blackwell issues fma /
-// add / mul on both lanes at once. FTA_SCALAR_MATH build: two plain registers (for comparison).
-#ifdef FTA_SCALAR_MATH
-struct f32x2 { float lo, hi; };
-__device__ __forceinline__ f32x2 mk2(float lo, float hi) { return f32x2{lo, hi}; }
-__device__ __forceinline__ void un2(f32x2 v, float& lo, float& hi) { lo = v.lo; hi = v.hi; }
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-  return f32x2{fmaf(a.lo, b.lo, c.lo), fmaf(a.hi, b.hi, c.hi)};
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { return f32x2{a.lo + b.lo, a.hi + b.hi}; }
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return f32x2{a.lo * b.lo, a.hi * b.hi}; }
-#elif !defined(FTA_ASM_F32X2)
-// the compiler's own f32x2 intrinsics: it does the register pairing itself
+// Two fp32 lanes handled together: the compiler's own f32x2 intrinsics (it does the register
+// pairing itself); Blackwell issues fma / add / mul on both lanes with one instruction.
 typedef float2 f32x2;
 __device__ __forceinline__ f32x2 mk2(float lo, float hi) { return make_float2(lo, hi); }
 __device__ __forceinline__ void un2(f32x2 v, float& lo, float& hi) { lo = v.x; hi = v.y; }
 __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { return __ffma2_rn(a, b, c); }
 __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return __fmul2_rn(a, b); }
-#else
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 mk2(float lo, float hi) {
-  f32x2 r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void un2(f32x2 v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-  f32x2 r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
-  f32x2 r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-  f32x2 r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-#endif
 
 // pack two fp32 into bf16x2 / f16x2 (lo in the low half), round to nearest even
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

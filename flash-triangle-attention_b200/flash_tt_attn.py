@@ -15,7 +15,10 @@ Differences from the reference, all relaxations:
     need not be a power of two (line 618);
   * ``dO`` and non-dense inputs are made contiguous instead of asserted on (604-606);
   * dBias is accumulated in float32 in a fixed order (bit-reproducible) and rounded once,
-    instead of fp16 atomics (425-426);
+    instead of fp16 atomics (425-426); with bf16 inputs the forward also saves the 16 bits of O
+    that its rounding drops, so that delta = rowsum(dO * O) - and with it dBias, a sum over all
+    L1 rows - keeps the accuracy the fp16 path has (costs one more saved tensor of q's size;
+    ``FTA_SAVE_O_RESIDUAL=0`` switches it off);
   * an optional ``group`` (a ``torch.distributed`` process group): q, k, v hold this rank's
     shard of the L1 rows, the bias is replicated, and the backward all-reduces the float32
     dBias over the group before rounding.
@@ -35,28 +38,54 @@ __all__ = ["attention", "attention_fwd_bwd_streamed", "reference_tt_attn", "chec
            "last_dbias_f32", "shard_plan", "shard_rows"]
 
 _DEBUG = os.environ.get("FTA_DEBUG", "0") == "1"
+_SAVE_O_RESIDUAL = os.environ.get("FTA_SAVE_O_RESIDUAL", "1") != "0"
 _status_words = {}
 _last = {"dbias_f32": None}
 
 
-def _status(device) -> torch.Tensor:
+class _Status:
+    """Per-device status word of the kernels plus a pinned host mirror of it.
+
+    The kernels never trap: a bounded device-side wait that runs out writes a code to ``word`` and
+    the launch returns with unfinished outputs. After every call of this module the word is copied
+    to ``mirror`` on the stream (4 bytes, no synchronisation); the next call looks at the mirror
+    on the host before it launches anything, so a failure surfaces as an exception at most one
+    call late without the hot path ever waiting for the device."""
+
+    def __init__(self, device):
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+    def publish(self):
+        self.mirror.copy_(self.word, non_blocking=True)
+
+    def raise_if_set(self, code=None):
+        code = int(self.mirror[0]) if code is None else code
+        if code != 0:
+            self.word.zero_()
+            self.mirror.zero_()
+            raise RuntimeError(f"flash_tt_attn: device status 0x{code:x} (a bounded device-side wait ran out "
+                               "in an earlier call; its outputs are incomplete)")
+
+
+def _status_of(device) -> _Status:
     key = (device.type, device.index)
     st = _status_words.get(key)
     if st is None:
-        st = torch.zeros(1, dtype=torch.int32, device=device)
-        _status_words[key] = st
+        st = _status_words[key] = _Status(device)
     return st
+
+
+def _status(device) -> torch.Tensor:
+    return _status_of(device).word
 
 
 def check_device_status(device=None) -> None:
     """Raise if a kernel of this module reported a device-side error (a bounded wait that ran
     out). Synchronises the device's current stream."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    st = _status(device)
-    code = int(st.item())
-    if code != 0:
-        st.zero_()
-        raise RuntimeError(f"flash_tt_attn: device status 0x{code:x} (a bounded device-side wait ran out)")
+    st = _status_of(device)
+    st.raise_if_set(int(st.word.item()))
 
 
 def last_dbias_f32():
@@ -90,25 +119,31 @@ class _attention(torch.autograd.Function):
         assert b_pw.shape == (B, H, L2, L2), "bias must be (B, H, L2, L2)"
         assert L2 % 128 == 0, "L2 must be a multiple of 128"
 
+        st = _status_of(q.device)
+        st.raise_if_set()  # an earlier call's device-side failure, seen through the host mirror
         q, k, v, b_pw = _dense(q), _dense(k), _dense(v), _dense(b_pw)
         o = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((3, B, H, L1, L2), dtype=torch.float32, device=q.device)  # softmax statistics
-        status = _status(q.device)
+        # the bits of O that rounding to bf16 drops, for the backward's delta (fp16 keeps enough)
+        need_bwd = any(ctx.needs_input_grad[:4])
+        o_res = torch.empty_like(o) if (need_bwd and _SAVE_O_RESIDUAL and q.dtype == torch.bfloat16) else None
         prob = _problem(q)
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream().cuda_stream
             check(_cabi.lib().fta_forward(prob, t5(q), t5(k), t5(v), t4(b_pw), float(sm_scale), t5(o),
-                                          lse.data_ptr(), status.data_ptr(), stream), "fta_forward")
+                                          None if o_res is None else o_res.data_ptr(),
+                                          lse.data_ptr(), st.word.data_ptr(), stream), "fta_forward")
+            st.publish()
         if _DEBUG:
             check_device_status(q.device)
-        ctx.save_for_backward(q, k, v, o, b_pw, lse)
+        ctx.save_for_backward(q, k, v, o, b_pw, lse, o_res)
         ctx.sm_scale = float(sm_scale)
         ctx.group = group
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, b_pw, lse = ctx.saved_tensors
+        q, k, v, o, b_pw, lse, o_res = ctx.saved_tensors
         assert do.dtype == q.dtype
         do = _dense(do)
         B, H, L1, L2, D = q.shape
@@ -123,11 +158,14 @@ class _attention(torch.autograd.Function):
         L = _cabi.lib()
         ws_bytes = int(L.fta_bwd_workspace_bytes(prob))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        status = _status(dev)
+        st = _status_of(dev)
+        st.raise_if_set()
+        status = st.word
         sharded = ctx.group is not None
         with torch.cuda.device(dev):
             stream = torch.cuda.current_stream().cuda_stream
-            check(L.fta_bwd_preprocess(prob, t5(o), t5(do), delta.data_ptr(), stream), "fta_bwd_preprocess")
+            check(L.fta_bwd_preprocess(prob, t5(o), None if o_res is None else o_res.data_ptr(), t5(do),
+                                       delta.data_ptr(), stream), "fta_bwd_preprocess")
             check(L.fta_backward(prob, t5(q), t5(k), t5(v), t4(b_pw), t5(do), lse.data_ptr(), delta.data_ptr(),
                                  ctx.sm_scale, t5(dq), t5(dk), t5(dv), db32.data_ptr(),
                                  None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
@@ -137,6 +175,7 @@ class _attention(torch.autograd.Function):
                 torch.distributed.all_reduce(db32, op=torch.distributed.ReduceOp.SUM, group=ctx.group)
                 check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
                       "fta_dbias_cast")
+            st.publish()
         if _DEBUG:
             check_device_status(dev)
         _last["dbias_f32"] = db32

@@ -21,7 +21,10 @@
  *    caller's status word (see fta_read_status) and the kernel returns;
  *  - supported: dtype fp16 / bf16 (q, k, v, bias, o, dO and the gradients share it),
  *    D in {32, 64}, L2 a multiple of 128, any L1 >= 1 (L1 != L2 is fine: a shard of rows),
- *    innermost (D) stride 1 and 16-byte aligned rows.
+ *    innermost (D) stride 1 and 16-byte aligned rows;
+ *  - every device pointer handed to the library (tensors, lse, delta, dBias buffers, the optional
+ *    residual) must be 16-byte aligned, the workspace 256-byte aligned: FTA_ERR_ALIGN /
+ *    FTA_ERR_WORKSPACE otherwise (the kernels move data with 16-byte vectors and bulk copies).
  */
 #ifndef FTA_H_
 #define FTA_H_
@@ -48,7 +51,7 @@ enum {
   FTA_ERR_HEAD_DIM = -3,   /* D not in {32, 64} */
   FTA_ERR_DTYPE = -4,      /* dtype not FTA_FP16 / FTA_BF16 */
   FTA_ERR_STRIDE = -5,     /* D stride != 1, or a stride that is not a multiple of 8 elements */
-  FTA_ERR_ALIGN = -6,      /* base pointer not 16-byte aligned */
+  FTA_ERR_ALIGN = -6,      /* a device pointer that is not 16-byte aligned */
   FTA_ERR_WORKSPACE = -7,  /* workspace too small */
   FTA_ERR_TENSOR_MAP = -8, /* the driver refused a TMA tensor map */
   FTA_ERR_CUDA = -9,       /* a CUDA runtime call failed (see fta_last_cuda_error) */
@@ -92,15 +95,22 @@ FTA_API int fta_last_cuda_error(void);
  * fully masked with a large negative bias (|max| ~ 1e9). Plane 2 holds that combination,
  * plane0*log2(e) + plane1, for rows with |max| <= 1e4 (the backward pass then needs one
  * statistic per row) and NaN for the others (the backward pass uses planes 0 and 1).
+ * `o_resid` is optional (NULL: not written): a buffer with the dtype and the strides of `o` that
+ * receives the part of O lost when it is rounded to 16 bits, dtype(O_f32 - dtype(O_f32)). Handed
+ * to fta_bwd_preprocess it makes delta = rowsum(dO * O) as if O had 16 mantissa bits; with bf16
+ * and O rounded to 8 bits the error of delta alone costs about 0.01 max-abs in a dBias summed
+ * over several hundred rows. The reference has no such output (it is fp16 only).
  * `status` points to one int32 the caller zeroed. */
 FTA_API int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
                 const FtaTensor5* v, const FtaTensor4* bias, float sm_scale,
-                const FtaTensor5* o, float* lse, int32_t* status, void* stream);
+                const FtaTensor5* o, void* o_resid, float* lse, int32_t* status, void* stream);
 
 /* Backward preprocess. Replaces `_attn_bwd_preprocess` (flash_tt_attn.py:266-288, launched
- * at 636-641): delta[b,h,i,j] = sum_d O[b,h,i,j,d] * dO[b,h,i,j,d], float32 contiguous. */
-FTA_API int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const FtaTensor5* dout,
-                       float* delta, void* stream);
+ * at 636-641): delta[b,h,i,j] = sum_d O[b,h,i,j,d] * dO[b,h,i,j,d], float32 contiguous.
+ * `o_resid` (may be NULL) is the residual fta_forward wrote, laid out like `o`: when given,
+ * O + residual takes the place of O. */
+FTA_API int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const void* o_resid,
+                       const FtaTensor5* dout, float* delta, void* stream);
 
 /* Bytes of workspace fta_backward needs for `prob` (a float32 dQ accumulator and the
  * partial dBias planes). 256-byte aligned workspace required. */
@@ -141,7 +151,9 @@ FTA_API int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype
  *    that device current); make that first call before any stream capture.
  *  - All calls on a device share the one array: two calls whose work overlaps on the GPU
  *    (different streams, different threads) race on it. Keep them on one stream, or order them.
- *    The array keeps what the last call wrote; each call clears or overwrites what it reads. */
+ *    The array keeps what the last call wrote; each call clears or overwrites what it reads.
+ *  - The looked-up address is cached per device for the life of the process; it does not survive
+ *    a cudaDeviceReset of that device. */
 FTA_API int fta_backward_noalloc(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
                                  const FtaTensor5* v, const FtaTensor4* bias, const FtaTensor5* dout,
                                  const float* lse, const float* delta, float sm_scale,

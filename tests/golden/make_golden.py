@@ -58,7 +58,9 @@ def load_reference_fn(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    ref_root = sys.argv[1]
     fn = load_reference_fn(ref_root)
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for name, cfg in CASES.items():

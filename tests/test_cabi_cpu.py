@@ -60,7 +60,7 @@ def _t4(ptr=0x1000, strides=(1 << 20, 1 << 14, 128, 1)):
 ])
 def test_forward_rejects_bad_problem_on_host(prob, code):
     lib = _cabi.lib()
-    rc = lib.fta_forward(prob, _t5(), _t5(), _t5(), _t4(), 1.0, _t5(), 0x2000, 0x3000, None)
+    rc = lib.fta_forward(prob, _t5(), _t5(), _t5(), _t4(), 1.0, _t5(), None, 0x2000, 0x3000, None)
     assert rc == code
 
 
@@ -68,15 +68,18 @@ def test_forward_rejects_bad_tensors_on_host():
     lib = _cabi.lib()
     prob = FtaProblem(1, 1, 4, 128, 32, 1)
     ok5, ok4 = _t5(), _t4()
-    assert lib.fta_forward(prob, _t5(ptr=0), ok5, ok5, ok4, 1.0, ok5, 0x2000, 0x3000, None) == -1
-    assert lib.fta_forward(prob, _t5(ptr=0x1004), ok5, ok5, ok4, 1.0, ok5, 0x2000, 0x3000, None) == -6
+    assert lib.fta_forward(prob, _t5(ptr=0), ok5, ok5, ok4, 1.0, ok5, None, 0x2000, 0x3000, None) == -1
+    assert lib.fta_forward(prob, _t5(ptr=0x1004), ok5, ok5, ok4, 1.0, ok5, None, 0x2000, 0x3000, None) == -6
     assert lib.fta_forward(prob, _t5(strides=(1 << 20, 1 << 18, 4096, 32, 2)), ok5, ok5, ok4, 1.0, ok5,
-                           0x2000, 0x3000, None) == -5
+                           None, 0x2000, 0x3000, None) == -5
     assert lib.fta_forward(prob, ok5, ok5, _t5(strides=(1 << 20, 1 << 18, 4100, 32, 1)), ok4, 1.0, ok5,
-                           0x2000, 0x3000, None) == -5
+                           None, 0x2000, 0x3000, None) == -5
     assert lib.fta_forward(prob, ok5, ok5, ok5, _t4(strides=(1 << 20, 1 << 14, 128, 2)), 1.0, ok5,
-                           0x2000, 0x3000, None) == -5
-    assert lib.fta_forward(prob, ok5, ok5, ok5, ok4, 1.0, ok5, None, 0x3000, None) == -1
+                           None, 0x2000, 0x3000, None) == -5
+    assert lib.fta_forward(prob, ok5, ok5, ok5, ok4, 1.0, ok5, None, None, 0x3000, None) == -1
+    # statistics and residual pointers must be 16-byte aligned too
+    assert lib.fta_forward(prob, ok5, ok5, ok5, ok4, 1.0, ok5, None, 0x2004, 0x3000, None) == -6
+    assert lib.fta_forward(prob, ok5, ok5, ok5, ok4, 1.0, ok5, 0x5008, 0x2000, 0x3000, None) == -6
 
 
 def test_backward_rejects_small_workspace_and_null():
@@ -93,6 +96,14 @@ def test_backward_rejects_small_workspace_and_null():
     assert args(0x10000, need - 1) == -7
     assert args(0x10010, need) == -7      # not 256-byte aligned
     assert args(None, need) == -1
+    # lse, delta and the dBias buffers are read / written with 16-byte vectors and bulk copies
+    bad = lambda lse, delta, db32, dbc: lib.fta_backward(prob, a5, a5, a5, a4, a5, lse, delta, 1.0, a5, a5, a5,
+                                                         db32, dbc, 0x10000, need, 0x3000, None)
+    assert bad(0x2004, 0x2100, 0x2200, None) == -6
+    assert bad(0x2000, 0x2108, 0x2200, None) == -6
+    assert bad(0x2000, 0x2100, 0x2204, None) == -6
+    assert bad(0x2000, 0x2100, 0x2200, 0x2302) == -6
+    assert lib.fta_bwd_preprocess(prob, a5, 0x4004, a5, 0x2100, None) == -6
     assert lib.fta_bwd_workspace_bytes(FtaProblem(1, 1, 4, 100, 32, 1)) == 0
 
 
@@ -101,4 +112,6 @@ def test_dbias_cast_argument_checks():
     assert lib.fta_dbias_cast(None, 0x1000, 16, 1, None) == -1
     assert lib.fta_dbias_cast(0x1000, 0x2000, 6, 1, None) == -2
     assert lib.fta_dbias_cast(0x1000, 0x2000, 16, 5, None) == -4
+    assert lib.fta_dbias_cast(0x1004, 0x2000, 16, 1, None) == -6
+    assert lib.fta_dbias_cast(0x1000, 0x2008, 16, 1, None) == -6
     assert lib.fta_read_status(None, None, None) == -1

@@ -29,8 +29,8 @@ def _setup():
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
     _cabi.check(L.fta_forward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), w.sm_scale, t5(o),
-                              lse.data_ptr(), status.data_ptr(), st), "fta_forward")
-    _cabi.check(L.fta_bwd_preprocess(prob, t5(o), t5(d["do"]), delta.data_ptr(), st), "fta_bwd_preprocess")
+                              None, lse.data_ptr(), status.data_ptr(), st), "fta_forward")
+    _cabi.check(L.fta_bwd_preprocess(prob, t5(o), None, t5(d["do"]), delta.data_ptr(), st), "fta_bwd_preprocess")
     return w, d, prob, L, lse, delta, status, st
 
 
