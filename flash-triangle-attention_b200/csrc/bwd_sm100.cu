@@ -12,10 +12,12 @@
 //   dV  += P^T dO, dK += dS^T Q                        (A operand read from TMEM)
 //   dQ   = dS K                                        (dS staged in smem, M-major)
 //
-// The tile is split in two 64-query halves, each with its own S^T / dP^T columns and barriers
-// and two compute warpgroups (one 32-query quarter each), so the tensor core works on one half
-// while the CUDA cores work on the other. The bias is read from a transposed copy (key-major)
-// so that the thread that owns a key row reads its query columns with 16-byte shared-memory loads.
+// Four compute warpgroups own one 32-query quarter of the tile each and move in step: one barrier
+// per phase collects all sixteen warps, and the issuer answers each with one batch of MMAs (after
+// phase 1: dV of this tile and S^T of the NEXT one; after phase 2: dK and the next dP^T), so the
+// operands of the next phase are always a whole phase ahead and no warpgroup ever waits for
+// another one's share of a tile. The bias is read from a transposed copy (key-major) so that the
+// thread that owns a key row reads its query columns with 16-byte shared-memory loads.
 //
 // dBias: each thread owns one key column and 32 query rows of the (jb,kb) tile and sums dS
 // (float32, before rounding) over the G rows in registers. At the end of a query block each
@@ -68,11 +70,11 @@ struct BwdCfg {
   static constexpr int B_QDOEMPTY = B_QDOFULL + NQ;
   static constexpr int B_BIASFULL = B_QDOEMPTY + NQ;
   static constexpr int B_BIASEMPTY = B_BIASFULL + 2;
-  static constexpr int B_SFULL = B_BIASEMPTY + 2;
-  static constexpr int B_DPFULL = B_SFULL + 2;
-  static constexpr int B_P1FULL = B_DPFULL + 2;
-  static constexpr int B_P2FULL = B_P1FULL + 2;
-  static constexpr int B_DQDONE = B_P2FULL + 2;
+  static constexpr int B_SFULL = B_BIASEMPTY + 2;   // S^T of the next tile is in TMEM
+  static constexpr int B_DPFULL = B_SFULL + 1;      // dP^T of the next tile is in TMEM
+  static constexpr int B_P1FULL = B_DPFULL + 1;     // all sixteen compute warps have written P^T
+  static constexpr int B_P2FULL = B_P1FULL + 1;     // ... dS^T (TMEM and the shared-memory staging tile)
+  static constexpr int B_DQDONE = B_P2FULL + 1;
   static constexpr int B_ACCFULL = B_DQDONE + 1;
   static constexpr int B_ACCFREE = B_ACCFULL + 1;
   static constexpr int B_DQSFULL = B_ACCFREE + 1;
@@ -170,11 +172,11 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(bar(C::B_BIASEMPTY + i), 1);   // store warp, once the boxes parked in the stage are read
       mbar_init(bar(C::B_FLA + i), 4);         // the four warps of the warpgroup that wrote the box
       mbar_init(bar(C::B_FLB + i), 4);
-      mbar_init(bar(C::B_SFULL + i), 1);
-      mbar_init(bar(C::B_DPFULL + i), 1);
-      mbar_init(bar(C::B_P1FULL + i), 8);  // one arrive per warp of the two warpgroups of a half
-      mbar_init(bar(C::B_P2FULL + i), 8);
     }
+    mbar_init(bar(C::B_SFULL), 1);
+    mbar_init(bar(C::B_DPFULL), 1);
+    mbar_init(bar(C::B_P1FULL), 16);  // one arrive per compute warp
+    mbar_init(bar(C::B_P2FULL), 16);
     mbar_init(bar(C::B_DQDONE), 1);
     mbar_init(bar(C::B_ACCFULL), 1);
     mbar_init(bar(C::B_ACCFREE), 16);
@@ -267,80 +269,109 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
     } else if (warp == 0) {
       // ---------------------------------------------------------------- MMA issuer
-      // Two hand-overs per tile and half: after phase 1 (P^T written) it issues dV and the next
-      // tile's S^T of that half; after phase 2 (dS^T written) dK and the next tile's dP^T. The
-      // next S^T / dP^T are therefore in flight while the compute warps are still busy.
+      // Two hand-overs per tile: after phase 1 (P^T written) it issues dV and the next tile's S^T;
+      // after phase 2 (dS^T written) dK and the next tile's dP^T. The next S^T / dP^T are therefore
+      // in flight while the compute warps work through the other phase.
       constexpr int fmt = kBf16 ? 1 : 0;
-      constexpr uint32_t idesc_s = umma_idesc_f16(fmt, 128, 64, 0, 0);    // S^T, dP^T halves
       constexpr uint32_t idesc_acc = umma_idesc_f16(fmt, 128, kD, 0, 1);  // dV, dK (A in TMEM, B M-major)
       const uint32_t sKV_a = smem_u32(sKV), sQDO_a = smem_u32(sQDO);
       bool ok = true;
       int tt = 0;
-      // S^T_w (which == 0) or dP^T_w (which == 1) of the tile with ring index `tix`, row g
-      auto issue_half = [&](int which, int tix, int g, int wh) {
-        const uint32_t st = sQDO_a + (tix % C::NQ) * C::STAGE_B;
-        const uint64_t dA = umma_smem_desc(sKV_a + g * 2 * C::TILE_B + which * C::TILE_B, 16, C::SBO, C::SWZ);
-        const uint64_t dB = umma_smem_desc(st + which * C::TILE_B + wh * 64 * C::ROW_B, 16, C::SBO, C::SWZ);
-        const uint32_t td = tbase + (which ? C::TM_DP : C::TM_ST) + wh * 64;
-        if (elect_one()) {
-#pragma unroll
-          for (int ks = 0; ks < kD / 16; ++ks) umma_ss(td, dA + ks * 2, dB + ks * 2, idesc_s, ks > 0);
-          umma_commit(bar((which ? C::B_DPFULL : C::B_SFULL) + wh));
-        }
-        __syncwarp();
-      };
-      // dV_g += P^T_w dO_w (which == 0) or dK_g += dS^T_w Q_w (which == 1)
-      auto issue_acc = [&](int which, int tix, int g, int wh, uint32_t acc_first) {
-        const uint32_t st = sQDO_a + (tix % C::NQ) * C::STAGE_B;
-        const uint64_t dB =
-            umma_smem_desc(st + (which ? 0 : C::TILE_B) + wh * 64 * C::ROW_B, C::SBO, C::SBO, C::SWZ);
-        const uint32_t td = tbase + C::TM_ACC + g * 2 * kD + (which ? 0 : kD);
-        const uint32_t ta = tbase + (which ? C::TM_DP : C::TM_ST) + wh * 64;
-        if (elect_one()) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_ts(td, ta + (ks >> 1) * 32 + (ks & 1) * 8, dB + ks * ((2 * C::SBO) >> 4), idesc_acc,
-                    ks > 0 ? 1u : acc_first);
-        }
-        __syncwarp();
-      };
+      constexpr uint32_t idesc_full = umma_idesc_f16(fmt, 128, 128, 0, 0);  // S^T, dP^T: all 128 queries
+      // Descriptors are built from 32-bit low words (address and leading-dimension offset; the high
+      // word is a compile-time constant) at the top of a tile, BEFORE the waits, so that a hand-over
+      // is wait -> fence -> ten tcgen05.mma + commit back to back by one elected lane.
+      constexpr uint32_t HI = (C::SBO >> 4) | (1u << 14) | (static_cast<uint32_t>(C::SWZ) << 29);
+      auto mk = [](uint32_t lo) { return (static_cast<uint64_t>(HI) << 32) | lo; };
+      auto lo_k = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); };            // K-major: lbo = 16 bytes
+      auto lo_m = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | ((C::SBO >> 4) << 16); };  // M-major: lbo = SBO
+      constexpr uint32_t KSTEP = (2 * C::SBO) >> 4;  // 16 rows further (M-major operand), in descriptor units
+      int slot = 0;  // ring slot of tile tt
+      uint32_t ring_par = 0;
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = row_begin + n * G;
         const int Gc = min(G, row_end - i0);
         const int T = nq * Gc;
-        ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32) &&
-             mbar_wait_warp(bar(C::B_QDOFULL + tt % C::NQ), (tt / C::NQ) & 1, w, 0x31);
+        ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x32) && mbar_wait_warp(bar(C::B_QDOFULL + slot), ring_par, w, 0x31);
         if (!ok) break;
         tc_fence_after_sync();
-        issue_half(0, tt, 0, 0);
-        issue_half(0, tt, 0, 1);
-        issue_half(1, tt, 0, 0);
-        issue_half(1, tt, 0, 1);
+        {
+          const uint32_t st = sQDO_a + slot * C::STAGE_B;
+          if (elect_one()) {
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+              const uint64_t dA = mk(lo_k(sKV_a + which * C::TILE_B)), dB = mk(lo_k(st + which * C::TILE_B));
+              const uint32_t td = tbase + (which ? C::TM_DP : C::TM_ST);
+#pragma unroll
+              for (int ks = 0; ks < kD / 16; ++ks) umma_ss(td, dA + ks * 2, dB + ks * 2, idesc_full, ks > 0);
+              umma_commit(bar(which ? C::B_DPFULL : C::B_SFULL));
+            }
+          }
+          __syncwarp();
+        }
+        int g = 0, jb = 0;
         for (int t = 0; t < T && ok; ++t, ++tt) {
-          const int jb = t / Gc, g = t % Gc, gn = (t + 1) % Gc;
           const bool more = t + 1 < T;
-          for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 1 done: dV, then the next S^T
-            ok = mbar_wait_warp(bar(C::B_P1FULL + wh), tt & 1, w, 0x33);
-            if (ok && t == 0 && wh == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
-            if (ok && more && wh == 0) {
-              ok = mbar_wait_warp(bar(C::B_QDOFULL + (tt + 1) % C::NQ), ((tt + 1) / C::NQ) & 1, w, 0x35);
-            }
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_acc(0, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
-            if (more) issue_half(0, tt + 1, gn, wh);
+          int gn = g + 1;
+          if (gn == Gc) gn = 0;
+          int slot_n = slot + 1;
+          uint32_t par_n = ring_par;
+          if (slot_n == C::NQ) {
+            slot_n = 0;
+            par_n ^= 1u;
           }
-          for (int wh = 0; wh < 2 && ok; ++wh) {  // phase 2 done: dK, then the next dP^T
-            ok = mbar_wait_warp(bar(C::B_P2FULL + wh), tt & 1, w, 0x39);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_acc(1, tt, g, wh, (jb > 0 || wh > 0) ? 1u : 0u);
-            if (wh == 1) {  // every MMA that reads this Q/dO stage has been issued
-              if (elect_one()) umma_commit(bar(C::B_QDOEMPTY + tt % C::NQ));
-              __syncwarp();
+          const uint32_t par = tt & 1;
+          const uint32_t accf = jb > 0 ? 1u : 0u;
+          const uint32_t st = sQDO_a + slot * C::STAGE_B, stn = sQDO_a + slot_n * C::STAGE_B;
+          const uint32_t kvn = sKV_a + gn * 2 * C::TILE_B;
+          const uint32_t tacc = tbase + C::TM_ACC + g * 2 * kD;
+          const uint32_t lo_dO = lo_m(st + C::TILE_B), lo_Q = lo_m(st);
+          const uint32_t lo_Kn = lo_k(kvn), lo_Vn = lo_k(kvn + C::TILE_B);
+          const uint32_t lo_Qn = lo_k(stn), lo_dOn = lo_k(stn + C::TILE_B);
+          asm volatile("" ::"r"(lo_dO), "r"(lo_Q), "r"(lo_Kn), "r"(lo_Vn), "r"(lo_Qn), "r"(lo_dOn), "r"(tacc));
+          // phase 1 done: dV, then the next S^T
+          ok = mbar_wait_warp(bar(C::B_P1FULL), par, w, 0x33);
+          if (ok && t == 0 && n > 0) ok = mbar_wait_warp(bar(C::B_ACCFREE), (n - 1) & 1, w, 0x34);
+          if (ok && more) ok = mbar_wait_warp(bar(C::B_QDOFULL + slot_n), par_n, w, 0x35);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (elect_one()) {
+            const uint64_t dB = mk(lo_dO);
+            const uint32_t ta = tbase + C::TM_ST;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              umma_ts(tacc + kD, ta + (ks >> 1) * 32 + (ks & 1) * 8, dB + ks * KSTEP, idesc_acc, ks > 0 ? 1u : accf);
+            if (more) {
+              const uint64_t dA = mk(lo_Kn), dQn = mk(lo_Qn);
+#pragma unroll
+              for (int ks = 0; ks < kD / 16; ++ks) umma_ss(ta, dA + ks * 2, dQn + ks * 2, idesc_full, ks > 0);
+              umma_commit(bar(C::B_SFULL));
             }
-            if (more) issue_half(1, tt + 1, gn, wh);
           }
+          __syncwarp();
+          // phase 2 done: dK, then the next dP^T
+          ok = mbar_wait_warp(bar(C::B_P2FULL), par, w, 0x39);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (elect_one()) {
+            const uint64_t dB = mk(lo_Q);
+            const uint32_t ta = tbase + C::TM_DP;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+              umma_ts(tacc, ta + (ks >> 1) * 32 + (ks & 1) * 8, dB + ks * KSTEP, idesc_acc, ks > 0 ? 1u : accf);
+            umma_commit(bar(C::B_QDOEMPTY + slot));  // every MMA that reads this Q/dO stage has been issued
+            if (more) {
+              const uint64_t dA = mk(lo_Vn), dOn = mk(lo_dOn);
+#pragma unroll
+              for (int ks = 0; ks < kD / 16; ++ks) umma_ss(ta, dA + ks * 2, dOn + ks * 2, idesc_full, ks > 0);
+              umma_commit(bar(C::B_DPFULL));
+            }
+          }
+          __syncwarp();
+          slot = slot_n;
+          ring_par = par_n;
+          g = gn;
+          if (gn == 0) ++jb;
         }
         if (ok) {
           if (elect_one()) {
@@ -352,7 +383,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       }
     } else if (warp == 2) {
       // ---------------------------------------------------------------- dQ issuer
-      // dQ = dS K needs the dS rows of both halves; it writes its own TMEM columns and reads no
+      // dQ = dS K needs the dS rows of all four quarters; it writes its own TMEM columns and reads no
       // Q/dO stage, so it is issued from a second warp and does not hold up the main issuer.
       constexpr uint32_t idesc_dq = umma_idesc_f16(kBf16 ? 1 : 0, 128, kD, 1, 1);  // A, B M-major
       const uint32_t sKV_a = smem_u32(sKV), sDS_a = smem_u32(sDS);
@@ -365,8 +396,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         ok = mbar_wait_warp(bar(C::B_KVFULL), n & 1, w, 0x36);
         for (int t = 0; t < T && ok; ++t, ++tt) {
           const int g = t % Gc;
-          ok = mbar_wait_warp(bar(C::B_P2FULL + 0), tt & 1, w, 0x37) &&
-               mbar_wait_warp(bar(C::B_P2FULL + 1), tt & 1, w, 0x38);
+          ok = mbar_wait_warp(bar(C::B_P2FULL), tt & 1, w, 0x37);
           if (!ok) break;
           tc_fence_after_sync();
           const uint64_t dSm = umma_smem_desc(sDS_a, 16384, 1024, kSwz128);
@@ -550,7 +580,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             ring_phase ^= 1u;
           }
           const uint8_t* st = sQDO + s * C::STAGE_B;
-          ok = mbar_wait_warp(bar(C::B_SFULL + wh), tt & 1, w, 0x42);
+          ok = mbar_wait_warp(bar(C::B_SFULL), tt & 1, w, 0x42);
           if (!ok) break;
           ok = mbar_wait_warp(bar(C::B_QDOFULL + s), ring_par, w, 0x43);  // statistics visible
           if (!ok) break;
@@ -633,9 +663,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tmem_st_wait();
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar(C::B_P1FULL + wh));
+          if (lane == 0) mbar_arrive(bar(C::B_P1FULL));
           // ---- phase 2: dS^T = P^T * (dP^T - delta), summed into the dBias registers
-          ok = mbar_wait_warp(bar(C::B_DPFULL + wh), tt & 1, w, 0x47);
+          ok = mbar_wait_warp(bar(C::B_DPFULL), tt & 1, w, 0x47);
           if (!ok) break;
           tc_fence_after_sync();
           uint32_t dd[16];  // dS^T of this key row, 32 queries, packed 16-bit pairs
@@ -692,7 +722,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) {
-            mbar_arrive(bar(C::B_P2FULL + wh));
+            mbar_arrive(bar(C::B_P2FULL));
             if (stage_dq) mbar_arrive(bar(C::B_DQSFULL));
           }
           if (!C::DQ_TMA && !(jb == 0 && g == 0)) {
@@ -756,7 +786,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         // their bias values; waiting for their phase-2 arrival rather than the earlier phase-1 one
         // also keeps the two warpgroups of the half in step, which measures faster), the second
         // one that half's part of the dS tile (free once the last dQ MMA has read it).
-        if (sub == 0) ok = mbar_wait_warp(bar(C::B_P2FULL + wh), (tt - 1) & 1, w, 0x49);
+        if (sub == 0) ok = mbar_wait_warp(bar(C::B_P2FULL), (tt - 1) & 1, w, 0x49);
         else ok = mbar_wait_warp(bar(C::B_DQDONE), (tt - 1) & 1, w, 0x4a);
         if (!ok) break;
         {

@@ -20,7 +20,7 @@ _lib = None
 def build(force: bool = False) -> str:
     if (not force) and os.path.exists(_LIB) and os.path.getmtime(_LIB) >= os.path.getmtime(_SRC):
         return _LIB
-    cmd = ["gcc", "-O3", "-fopenmp", "-shared", "-fPIC", "-o", _LIB, _SRC, "-lm"]
+    cmd = ["gcc", "-O3", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", "-o", _LIB, _SRC, "-lm"]
     subprocess.run(cmd, check=True)
     return _LIB
 

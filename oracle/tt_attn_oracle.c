@@ -9,12 +9,12 @@
  *   dQ = sm_scale dS K, dK = sm_scale dS^T Q, dBias[b,h,j,k] = sum_i dS[b,h,i,j,k].
  *
  * Inputs and outputs are float32, row-major contiguous, q/k/v/o/do of shape
- * (B,H,L1,L2,D) and bias of shape (B,H,L2,L2). All sums are carried in double, so the
- * result is the correctly rounded answer for the float32 inputs to well below the
- * tolerances the tests use. Rows (b,h,i) run in parallel under OpenMP; dBias is reduced
+ * (B,H,L1,L2,D) and bias of shape (B,H,L2,L2). The logits are rounded to float32 where the
+ * reference's float32 tensors round them; all sums are carried in double, so the result is
+ * the reference's answer for the float32 inputs to well below the tolerances the tests use. Rows (b,h,i) run in parallel under OpenMP; dBias is reduced
  * over threads in a fixed order.
  *
- * Build: gcc -O3 -fopenmp -shared -fPIC (see build_oracle.py). Loaded through ctypes by
+ * Build: gcc -O3 -fopenmp -shared -fPIC (oracle/c_oracle.py: build()). Loaded through ctypes by
  * tests/, by the smoke check and by the benchmark's cpu_baseline leg only.
  */
 #include <math.h>
@@ -46,7 +46,15 @@ static void row_softmax(const float* q, const float* k, const float* bias, int L
       const float* kn = k + (size_t)n * D;
       double s = 0.0;
       for (int d = 0; d < D; ++d) s += (double)qj[d] * (double)kn[d];
-      s = s * scale + (double)bias[(size_t)j * L2 + n];
+      /* The reference forms the logits in the tensors' dtype before its float32 softmax:
+       * qk (853), qk * sm_scale (856), + bias (857), each a float32 tensor here. Those three
+       * roundings only matter for keys masked with a huge negative bias (-1e9 absorbs the
+       * q.k term entirely: a fully masked row gets the uniform distribution), and there they
+       * ARE the reference's answer, so they are reproduced; everything after is in double. */
+      const float qk = (float)s;
+      const float qk_scaled = qk * (float)scale;
+      const float logit = qk_scaled + bias[(size_t)j * L2 + n];
+      s = (double)logit;
       pj[n] = s;
       if (s > m) m = s;
     }

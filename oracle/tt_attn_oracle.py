@@ -37,6 +37,18 @@ def _chunk_rows(L1: int, L2: int, budget_elems: int = 1 << 24) -> int:
     return max(1, min(L1, budget_elems // max(1, L2 * L2)))
 
 
+def _logits(qk, bias_bh, sm_scale, dtype):
+    """qk * sm_scale + bias as the reference forms it: three float32 tensors in a row (qk, the
+    scaled qk, the sum with the bias; flash_tt_attn.py:853-857 on float32 inputs). The roundings
+    only matter where a huge negative bias (-1e9) absorbs the q.k term - a fully masked row gets the
+    uniform distribution - and there they are the reference's answer, so the float64 mode keeps
+    them too; everything after the logits is evaluated in ``dtype``."""
+    x = qk.astype(np.float32, copy=False)
+    x = x * np.float32(sm_scale)
+    x = x + bias_bh.astype(np.float32, copy=False)[None]
+    return x.astype(dtype, copy=False)
+
+
 def forward(q, k, v, bias, sm_scale, dtype=np.float32, return_lse=False):
     """O (and optionally the base-2 log-sum-exp the reference stores, flash_tt_attn.py:258).
 
@@ -58,8 +70,7 @@ def forward(q, k, v, bias, sm_scale, dtype=np.float32, return_lse=False):
             for i0 in range(0, L1, step):
                 i1 = min(L1, i0 + step)
                 x = np.matmul(q[b, h, i0:i1], k[b, h, i0:i1].transpose(0, 2, 1))  # (r, L2, L2)
-                x *= dtype(sm_scale)
-                x += bb[None]
+                x = _logits(x, bb, sm_scale, dtype)
                 m = x.max(axis=-1, keepdims=True)
                 np.subtract(x, m, out=x)
                 np.exp(x, out=x)
@@ -93,8 +104,7 @@ def forward_backward(q, k, v, bias, do, sm_scale, dtype=np.float32):
                 i1 = min(L1, i0 + step)
                 qq, kk, vv, dd = q[b, h, i0:i1], k[b, h, i0:i1], v[b, h, i0:i1], do[b, h, i0:i1]
                 x = np.matmul(qq, kk.transpose(0, 2, 1))
-                x *= sc
-                x += bb[None]
+                x = _logits(x, bb, sm_scale, dtype)
                 x -= x.max(axis=-1, keepdims=True)
                 np.exp(x, out=x)
                 x /= x.sum(axis=-1, keepdims=True)  # x = P

@@ -23,12 +23,16 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-# name -> (B, H, L, D, seed, std, sm_scale, mask_cols, full_outputs)
+# name -> (B, H, L, D, seed, std, sm_scale, masked key columns (> 0) or masked query rows (< 0), full_outputs)
 CASES = {
     "tiny_l16": (1, 2, 16, 16, 11, 1.0, 0.25, 0, True),
     "c1_cpu_l64": (1, 4, 64, 32, 0, 1.0, 1.0 / np.sqrt(32.0), 0, False),
     "testop_l32": (2, 2, 32, 32, 20, 0.5, 0.5, 0, False),  # distribution/scale of the reference's test_op
     "masked_l32": (1, 2, 32, 16, 7, 1.0, 0.25, 5, False),
+    # -1e9 on whole QUERY rows (what an ending-node call makes of masked key columns): every key of
+    # such a row is masked, the float32 logits lose the q.k term and the reference's answer is the
+    # uniform distribution over the keys
+    "maskedrows_l32": (1, 2, 32, 16, 9, 1.0, 0.25, -4, False),
 }
 SAMPLE_STRIDE = 37
 
@@ -42,9 +46,12 @@ def case_inputs(name):
     v = rng.standard_normal(shape, dtype=np.float32) * np.float32(std)
     do = rng.standard_normal(shape, dtype=np.float32)
     bias = rng.standard_normal((B, H, L, L), dtype=np.float32) * np.float32(std)
-    if mask_cols:
+    if mask_cols > 0:
         cols = rng.choice(np.arange(1, L), size=mask_cols, replace=False)
         bias[..., cols] += np.float32(-1e9)
+    elif mask_cols < 0:  # that many fully masked query rows
+        rows = rng.choice(np.arange(1, L), size=-mask_cols, replace=False)
+        bias[:, :, rows, :] += np.float32(-1e9)
     return q, k, v, do, bias, float(scale)
 
 
