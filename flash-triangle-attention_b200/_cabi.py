@@ -40,6 +40,7 @@ EXPORTS = (
     "fta_version", "fta_strerror", "fta_last_cuda_error", "fta_forward", "fta_bwd_preprocess",
     "fta_bwd_workspace_bytes", "fta_bwd_num_planes", "fta_backward", "fta_dbias_cast",
     "fta_read_status", "fta_profile_backward_kernel", "fta_backward_noalloc", "fta_noalloc_max_bytes",
+    "fta_memcpy_2d", "fta_mask_bias",
 )
 
 
@@ -77,6 +78,10 @@ def lib():
     L.fta_backward_noalloc.argtypes = [PP, P5, P5, P5, P4, P5, vp, vp, f32, P5, P5, P5, vp, vp, vp, vp]
     L.fta_noalloc_max_bytes.restype = ctypes.c_size_t
     L.fta_noalloc_max_bytes.argtypes = []
+    L.fta_mask_bias.restype = ctypes.c_int
+    L.fta_mask_bias.argtypes = [PP, P4, vp, vp, vp]
+    L.fta_memcpy_2d.restype = ctypes.c_int
+    L.fta_memcpy_2d.argtypes = [vp, ctypes.c_size_t, vp, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, vp]
     L.fta_profile_backward_kernel.restype = ctypes.c_int
     L.fta_profile_backward_kernel.argtypes = [vp, vp]
     _lib = L

@@ -21,7 +21,7 @@ bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0;
 int check_problem(const FtaProblem* p) {
   if (!p) return FTA_ERR_NULL;
   if (p->B <= 0 || p->H <= 0 || p->L1 <= 0 || p->L2 <= 0) return FTA_ERR_SHAPE;
-  if (p->L2 % 128 != 0) return FTA_ERR_SHAPE;
+  if (p->L2 % 8 != 0) return FTA_ERR_SHAPE;
   if (p->D != 32 && p->D != 64) return FTA_ERR_HEAD_DIM;
   if (p->dtype != FTA_FP16 && p->dtype != FTA_BF16) return FTA_ERR_DTYPE;
   if (static_cast<long long>(p->B) * p->H > 65535) return FTA_ERR_TOO_LARGE;
@@ -57,10 +57,18 @@ int map5(CUtensorMap* m, const FtaProblem* p, const FtaTensor5* t) {
   return fta::make_tmap_16bit(m, t->ptr, 5, dims, str, box, p->D * 2) == 0 ? FTA_OK : FTA_ERR_TENSOR_MAP;
 }
 
-// 4-D map over the bias (key, query, H, B); `box_k` keys x 128 queries per tile.
+int padded_l2(const FtaProblem* p) { return (p->L2 + 127) / 128 * 128; }
+
+// 4-D map over the bias (key, query, H, B); `box_k` keys x 128 queries per tile. The bias the kernels
+// read always spans whole 128-blocks: the caller's tensor when L2 is a multiple of 128, else the
+// padded copy made by fta_mask_bias.
 int map_bias(CUtensorMap* m, const FtaProblem* p, const FtaTensor4* t, int box_k, int swizzle) {
-  const uint64_t dims[4] = {static_cast<uint64_t>(p->L2), static_cast<uint64_t>(p->L2),
-                            static_cast<uint64_t>(p->H), static_cast<uint64_t>(p->B)};
+  const uint64_t l2p = static_cast<uint64_t>(padded_l2(p));
+  // a ragged problem must come with the padded copy: rows at least L2p apart, planes L2p rows apart
+  if (l2p != static_cast<uint64_t>(p->L2) &&
+      (static_cast<uint64_t>(t->stride[2]) < l2p || static_cast<uint64_t>(t->stride[1]) < l2p * l2p))
+    return FTA_ERR_STRIDE;
+  const uint64_t dims[4] = {l2p, l2p, static_cast<uint64_t>(p->H), static_cast<uint64_t>(p->B)};
   const uint64_t str[4] = {0, static_cast<uint64_t>(t->stride[2]) * 2, static_cast<uint64_t>(t->stride[1]) * 2,
                            static_cast<uint64_t>(t->stride[0]) * 2};
   const uint32_t box[4] = {static_cast<uint32_t>(box_k), 128, 1, 1};
@@ -89,7 +97,7 @@ const char* fta_strerror(int code) {
   switch (code) {
     case FTA_OK: return "ok";
     case FTA_ERR_NULL: return "a required pointer is NULL";
-    case FTA_ERR_SHAPE: return "bad shape: sizes must be positive and L2 a multiple of 128";
+    case FTA_ERR_SHAPE: return "bad shape: sizes must be positive and L2 a multiple of 8 (of 128 without fta_mask_bias)";
     case FTA_ERR_HEAD_DIM: return "unsupported head dimension: D must be 32 or 64";
     case FTA_ERR_DTYPE: return "unsupported dtype: fp16 or bf16 only";
     case FTA_ERR_STRIDE: return "bad stride: D stride must be 1, other strides positive multiples of 8 elements";
@@ -147,9 +155,30 @@ int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const void* 
     so[i] = o->stride[i];
     sd[i] = dout->stride[i];
   }
-  if (const int e = fta::launch_preprocess(o->ptr, o_resid, so, dout->ptr, sd, delta, prob->B, prob->H, prob->L1,
+  const int l2p = padded_l2(prob);
+  if (l2p != prob->L2) {
+    // the entries of queries past L2 (whole 128-blocks are read by the backward kernel) must be finite
+    const cudaError_t e = cudaMemsetAsync(delta, 0, sizeof(float) * static_cast<size_t>(prob->B) * prob->H * prob->L1 * l2p,
+                                          static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e);
+  }
+  if (const int e = fta::launch_preprocess(o->ptr, o_resid, so, dout->ptr, sd, delta, l2p, prob->B, prob->H, prob->L1,
                                            prob->L2, prob->D, prob->dtype == FTA_BF16,
                                            static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
+  return FTA_OK;
+}
+
+int fta_mask_bias(const FtaProblem* prob, const FtaTensor4* bias, const uint8_t* key_mask, void* out, void* stream) {
+  int rc = check_problem(prob);
+  if (rc) return rc;
+  if ((rc = check_t4(bias))) return rc;
+  if (!out) return FTA_ERR_NULL;
+  if (!aligned16(out) || reinterpret_cast<uintptr_t>(key_mask) % 8 != 0) return FTA_ERR_ALIGN;
+  long long sb[4];
+  for (int i = 0; i < 4; ++i) sb[i] = bias->stride[i];
+  if (const int e = fta::launch_mask_bias(bias->ptr, sb, key_mask, out, prob->B, prob->H, prob->L2, padded_l2(prob),
+                                          prob->dtype == FTA_BF16, static_cast<cudaStream_t>(stream)))
     return cuda_fail(e);
   return FTA_OK;
 }
@@ -163,8 +192,9 @@ size_t fta_bwd_workspace_bytes(const FtaProblem* prob) {
   if (check_problem(prob)) return 0;
   const size_t rows = static_cast<size_t>(prob->B) * prob->H * prob->L1 * prob->L2;
   const size_t plane = static_cast<size_t>(prob->B) * prob->H * prob->L2 * prob->L2 * sizeof(float);
+  const size_t l2p = static_cast<size_t>(padded_l2(prob));
   return align256(rows * prob->D * sizeof(float)) + align256(plane * fta_bwd_num_planes(prob)) +
-         align256(plane / 2);  // + key-major copy of the bias (16-bit)
+         align256(static_cast<size_t>(prob->B) * prob->H * l2p * l2p * 2);  // + key-major copy of the bias (16-bit, whole blocks)
 }
 
 int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k, const FtaTensor5* v,
@@ -196,26 +226,28 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
   fta::BwdArgs a;
   FtaTensor4 bt;  // key-major copy: (B, H, key, query) contiguous
   bt.ptr = bias_t;
-  bt.stride[0] = static_cast<int64_t>(prob->H) * prob->L2 * prob->L2;
-  bt.stride[1] = static_cast<int64_t>(prob->L2) * prob->L2;
-  bt.stride[2] = prob->L2;
+  const int l2p = padded_l2(prob);
+  bt.stride[0] = static_cast<int64_t>(prob->H) * l2p * l2p;
+  bt.stride[1] = static_cast<int64_t>(l2p) * l2p;
+  bt.stride[2] = l2p;
   bt.stride[3] = 1;
   if ((rc = map5(&a.tmQ, prob, q)) || (rc = map5(&a.tmK, prob, k)) || (rc = map5(&a.tmV, prob, v)) ||
       (rc = map5(&a.tmDO, prob, dout)) || (rc = map_bias(&a.tmBiasT, prob, &bt, 64, 128)))
     return rc;
   {
-    // dq32 seen as (rows, D) float32; the kernel adds 128-row x 32-column tiles into it with TMA reductions
-    if (rows >= (1ull << 31)) return FTA_ERR_SHAPE;  // tile coordinates are signed 32-bit
-    const uint64_t dims[2] = {static_cast<uint64_t>(prob->D), rows};
-    const uint64_t str[2] = {0, static_cast<uint64_t>(prob->D) * 4};
-    const uint32_t box[2] = {32, 128};
-    if (fta::make_tmap(&a.tmDQ, 4, dq32, 2, dims, str, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
-    // the partial dBias planes, key-major: (nplanes * B*H * L2 key rows, L2 queries) float32
-    const uint64_t prow = static_cast<uint64_t>(nplanes) * prob->B * prob->H * prob->L2;
-    if (prow >= (1ull << 31)) return FTA_ERR_SHAPE;
-    const uint64_t pdims[2] = {static_cast<uint64_t>(prob->L2), prow};
-    const uint64_t pstr[2] = {0, static_cast<uint64_t>(prob->L2) * 4};
-    if (fta::make_tmap(&a.tmPlane, 4, planes, 2, pdims, pstr, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
+    // dq32 seen as (B*H*L1, L2, D) float32; the kernel adds 128-query x 32-column tiles into it with
+    // TMA reductions (the part of a ragged last query block beyond L2 is clipped)
+    const uint64_t bhi = static_cast<uint64_t>(prob->B) * prob->H * prob->L1;
+    if (bhi >= (1ull << 31)) return FTA_ERR_SHAPE;  // tile coordinates are signed 32-bit
+    const uint64_t dims[3] = {static_cast<uint64_t>(prob->D), static_cast<uint64_t>(prob->L2), bhi};
+    const uint64_t str[3] = {0, static_cast<uint64_t>(prob->D) * 4, static_cast<uint64_t>(prob->L2) * prob->D * 4};
+    const uint32_t box[3] = {32, 128, 1};
+    if (fta::make_tmap(&a.tmDQ, 4, dq32, 3, dims, str, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
+    // the partial dBias planes, key-major: (nplanes * B*H, L2 keys, L2 queries) float32, clipped alike
+    const uint64_t pdims[3] = {static_cast<uint64_t>(prob->L2), static_cast<uint64_t>(prob->L2),
+                               static_cast<uint64_t>(nplanes) * prob->B * prob->H};
+    const uint64_t pstr[3] = {0, static_cast<uint64_t>(prob->L2) * 4, static_cast<uint64_t>(prob->L2) * prob->L2 * 4};
+    if (fta::make_tmap(&a.tmPlane, 4, planes, 3, pdims, pstr, box, 128) != 0) return FTA_ERR_TENSOR_MAP;
   }
   a.lse = lse;
   a.delta = delta;
@@ -239,7 +271,7 @@ int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* 
 
   long long sb[4];
   for (int i = 0; i < 4; ++i) sb[i] = bias->stride[i];
-  if (const int e = fta::launch_bwd_prologue(bias->ptr, sb, bias_t, prob->B, prob->H, prob->L2, dq32,
+  if (const int e = fta::launch_bwd_prologue(bias->ptr, sb, bias_t, prob->B, prob->H, l2p, dq32,
                                              static_cast<long long>(rows) * prob->D, st))
     return cuda_fail(e);
   if (g_prof_start) cudaEventRecord(g_prof_start, st);
@@ -259,6 +291,16 @@ int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* 
   if (const int e = fta::launch_dbias_cast(src, n, dst, dtype == FTA_BF16, static_cast<cudaStream_t>(stream)))
     return cuda_fail(e);
   return FTA_OK;
+}
+
+int fta_memcpy_2d(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes, size_t width_bytes,
+                  size_t rows, void* stream) {
+  if (!dst || !src) return FTA_ERR_NULL;
+  if (width_bytes == 0 || rows == 0) return FTA_ERR_SHAPE;
+  if (dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes) return FTA_ERR_STRIDE;
+  const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch_bytes, src, src_pitch_bytes, width_bytes, rows,
+                                          cudaMemcpyDefault, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? FTA_OK : cuda_fail(e);
 }
 
 int fta_profile_backward_kernel(void* start_event, void* stop_event) {

@@ -43,8 +43,8 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kBwdThreads = 640;    // 4 service warps + 16 compute warps
-constexpr int kAuxRegs = 56;        // registers per thread of the service warpgroup
-constexpr int kComputeRegs = 104;   // 512 * 104 + 128 * 56 <= 640 * 96, the CTA's register allotment at launch
+constexpr int kAuxRegs = 64;        // registers per thread of the service warpgroup
+constexpr int kComputeRegs = 104;   // 512 * 104 + 128 * 64 == 640 * 96, the CTA's register allotment at launch
 
 template <int kD>
 struct BwdCfg {
@@ -106,6 +106,7 @@ struct BwdParams {
   void* dv;
   int* status;
   int H, L1, L2, NP, BH;
+  int stat_pitch;  // row pitch of lse / delta: L2 rounded up to 128
   long long sdk[4], sdv[4];
   float scale;  // sm_scale
   long long stat_stride;  // elements between the statistics planes
@@ -147,7 +148,9 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   auto bar = [&](int i) { return bar0 + 8u * static_cast<uint32_t>(i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nkb = p.L2 / 128, nq = p.L2 / 128;
+  // a ragged last block (L2 not a multiple of 128) is padded: loads fill zeros, the key-major bias
+  // copy holds -inf for keys past L2, the statistics give P = 0 for queries past L2, stores are clipped
+  const int nkb = (p.L2 + 127) / 128, nq = nkb;
   const int kb = blockIdx.x % nkb;
   const int r = (blockIdx.x / nkb) % p.NP;
   const int bh = blockIdx.x / (nkb * p.NP);
@@ -256,7 +259,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
               tma_load_5d_hint(smem_u32(st), &tmQ, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b, pol_stream);
               tma_load_5d_hint(smem_u32(st + C::TILE_B), &tmDO, bar(C::B_QDOFULL + s), 0, jb * 128, i0 + g, h, b,
                                pol_stream);
-              const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.L2 + jb * 128;
+              const long long roff = (static_cast<long long>(bh) * p.L1 + i0 + g) * p.stat_pitch + jb * 128;
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B), p.lse + roff, 512, bar(C::B_QDOFULL + s));
               bulk_load_1d(smem_u32(st + 2 * C::TILE_B + 512), p.lse + p.stat_stride + roff, 512,
                            bar(C::B_QDOFULL + s));
@@ -432,8 +435,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       auto dq_event = [&](int irow, int jblk) -> bool {
         if (!mbar_wait_warp(bar(C::B_DQSFULL), k & 1, w, 0x51)) return false;
         if (elect_one()) {
-          const long long row0 = (static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128;
-          tma_reduce_add_2d(&tmDQ, smem_u32(sDQ), 0, static_cast<int>(row0));
+          tma_reduce_add_3d(&tmDQ, smem_u32(sDQ), 0, jblk * 128, bh * p.L1 + irow);
           bulk_commit_group();
           bulk_wait_read_all();  // the staging tile has been read: the compute warps may refill it
           mbar_arrive(bar(C::B_DQSFREE));
@@ -445,7 +447,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       for (int n = 0; n < ngroups && ok; ++n) {
         const int i0 = row_begin + n * G;
         const int Gc = min(G, row_end - i0);
-        const int prow = (r * p.BH + bh) * p.L2 + kb * 128;  // first key row of this CTA's plane tile
+        const int pkey = kb * 128, pidx = r * p.BH + bh;  // first key row of this CTA's tile, its plane
         for (int jb = 0; jb < nq && ok; ++jb, ++nb) {
           if constexpr (C::DQ_TMA) {
             for (int g = 0; g < Gc && ok; ++g) {
@@ -463,8 +465,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int hh = 0; hh < 2; ++hh) {
               const uint32_t src = smem_u32(sDS + hh * 16384);
               const int qcol = jb * 128 + (2 * hh + 1) * 32;
-              if (n == 0) tma_store_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
-              else tma_reduce_add_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
+              if (n == 0) tma_store_3d_hint(&tmPlane, src, qcol, pkey, pidx, pol_keep);
+              else tma_reduce_add_3d_hint(&tmPlane, src, qcol, pkey, pidx, pol_keep);
             }
             bulk_commit_group();
           }
@@ -476,8 +478,8 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             for (int hh = 0; hh < 2; ++hh) {
               const uint32_t src = smem_u32(sBias + bs * C::BIAS_B + hh * 16384);
               const int qcol = jb * 128 + (2 * hh) * 32;
-              if (n == 0) tma_store_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
-              else tma_reduce_add_2d_hint(&tmPlane, src, qcol, prow, pol_keep);
+              if (n == 0) tma_store_3d_hint(&tmPlane, src, qcol, pkey, pidx, pol_keep);
+              else tma_reduce_add_3d_hint(&tmPlane, src, qcol, pkey, pidx, pol_keep);
             }
             bulk_commit_group();
             bulk_wait_read_le1();  // the older group (dS tile) has been read
@@ -548,11 +550,13 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         return true;
       }
       float* dst = p.dq32 + ((static_cast<long long>(bh) * p.L1 + irow) * p.L2 + jblk * 128 + key) * kD + qd * W;
+      const bool q_live = jblk * 128 + key < p.L2;  // here `key` is the TMEM lane = query row of the dQ tile
 #pragma unroll
       for (int c = 0; c < W / 8; ++c) {
         uint32_t qv[8];
         tmem_ld8(tbase + C::TM_DQ + buf * kD + qd * W + c * 8 + lane_off, qv);
         tmem_ld_wait();
+        if (!q_live) continue;
         red_add_v4(dst + c * 8, __uint_as_float(qv[0]), __uint_as_float(qv[1]), __uint_as_float(qv[2]),
                    __uint_as_float(qv[3]));
         red_add_v4(dst + c * 8 + 4, __uint_as_float(qv[4]), __uint_as_float(qv[5]), __uint_as_float(qv[6]),
@@ -594,7 +598,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           // up to 2^-9 * |dP - delta| into every term of the dBias sums over L1 (0.04 max-abs at
           // 768 rows of N(0,1) inputs, twice the tolerance); fp16 keeps 11 bits for 16 conversions
           // per thread and tile.
-          uint32_t ph[16], pp[16];
+          uint32_t ph[16], pp[8];  // pp: one half of the quarter at a time (two 8-column stores)
           const float4* c4 = reinterpret_cast<const float4*>(st + 2 * C::TILE_B + 1536) + qd * 8;
           // one lane per query of the quarter looks at c: NaN = a row that needs the two-part form
           const float cq = reinterpret_cast<const float*>(st + 2 * C::TILE_B + 1536)[qd * 32 + lane];
@@ -622,10 +626,13 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                          fma2(mk2(b0, b1), log2e2, c2[e])),
                     y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-                pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                pp[(ch & 1) * 4 + e] = pack2<kBf16>(p0, p1);
+                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[(ch & 1) * 4 + e];
               }
               if (ch + 1 < NCH) tmem_ld_wait();
+              // the 16 columns of queries 0-15 (16-31) have been read: P^T of those queries goes over
+              // the first (second) 8 of them
+              if (ch & 1) tmem_st8(tST + (ch >> 1) * 8, pp);
             }
           } else {
 #pragma unroll
@@ -653,13 +660,13 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                                      mk2(b0, b1));
                 un2(fma2(add2(x, nm2[e]), log2e2, nl2[e]), y0, y1);
                 const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-                pp[ch * 4 + e] = pack2<kBf16>(p0, p1);
-                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[ch * 4 + e];
+                pp[c8 * 4 + e] = pack2<kBf16>(p0, p1);
+                ph[ch * 4 + e] = kBf16 ? pack_f16x2(p0, p1) : pp[c8 * 4 + e];
               }
             }
+            tmem_st8(tST + c16 * 8, pp);
           }
           }
-          tmem_st16(tST, pp);  // all 32 columns have been read: P^T goes over the first 16
           tmem_st_wait();
           tc_fence_before_sync();
           __syncwarp();
@@ -755,6 +762,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             uint16_t* base = reinterpret_cast<uint16_t*>(wh == 0 ? p.dv : p.dk) + b * sd[0] + h * sd[1] +
                              static_cast<long long>(kb * 128 + key) * sd[3];
             const float mul = (wh == 0) ? 1.0f : p.scale;
+            const bool key_live = kb * 128 + key < p.L2;  // keys past L2 in a ragged block own no output row
             for (int g = sub; g < Gc; g += 2) {
               uint16_t* optr = base + static_cast<long long>(i0 + g) * sd[2];
               const uint32_t ta = tbase + C::TM_ACC + g * 2 * kD + (wh == 0 ? kD : 0) + lane_off;
@@ -770,7 +778,7 @@ fta_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                   ov.y = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 2]) * mul, __uint_as_float(av[v4 * 8 + 3]) * mul);
                   ov.z = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 4]) * mul, __uint_as_float(av[v4 * 8 + 5]) * mul);
                   ov.w = pack2<kBf16>(__uint_as_float(av[v4 * 8 + 6]) * mul, __uint_as_float(av[v4 * 8 + 7]) * mul);
-                  *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
+                  if (key_live) *reinterpret_cast<uint4*>(optr + c * 32 + v4 * 8) = ov;
                 }
               }
             }
@@ -839,8 +847,9 @@ int launch_bwd_t(const BwdArgs& a, int NP, cudaStream_t stream) {
     p.sdv[i] = a.sdv[i];
   }
   p.scale = a.sm_scale;
-  p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
-  const int grid = a.B * a.H * NP * (a.L2 / 128);
+  p.stat_pitch = (a.L2 + 127) / 128 * 128;
+  p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * p.stat_pitch;
+  const int grid = a.B * a.H * NP * ((a.L2 + 127) / 128);
   kern<<<grid, kBwdThreads, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmDO, a.tmBiasT, a.tmDQ, a.tmPlane, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -855,7 +864,7 @@ int bwd_rows_per_cta(int D) { return D == 32 ? BwdCfg<32>::G : BwdCfg<64>::G; }
 int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms) {
   const int G = bwd_rows_per_cta(D);
   const int ngroups = (L1 + G - 1) / G;
-  const long long base = static_cast<long long>(B) * H * (L2 / 128);
+  const long long base = static_cast<long long>(B) * H * ((L2 + 127) / 128);
   const int np_max = ngroups < 64 ? ngroups : 64;
   auto efficiency = [&](int np) {
     const long long ctas = base * np;

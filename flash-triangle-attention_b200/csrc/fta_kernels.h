@@ -51,8 +51,8 @@ int fwd_rows_per_cta(int D);
 
 struct BwdArgs {
   CUtensorMap tmQ, tmK, tmV, tmDO, tmBiasT;  // tmBiasT: over the key-major copy of the bias
-  CUtensorMap tmDQ;    // dq32 as a 2-D float32 tensor (rows, D), box 128 rows x 32 columns, 128 B swizzle
-  CUtensorMap tmPlane; // the partial dBias planes as (nplanes*B*H*L2 key rows, L2 queries) float32, same box
+  CUtensorMap tmDQ;    // dq32 as a 3-D float32 tensor (B*H*L1, L2, D), box 128 queries x 32 columns, 128 B swizzle
+  CUtensorMap tmPlane; // the partial dBias planes as (nplanes*B*H, L2 keys, L2 queries) float32, same box
   const float* lse;    // (3,B,H,L1,L2): -max, -log2(sum), combined (NaN where inexact)
   const float* delta;  // (B,H,L1,L2)
   float* dq32;         // (B,H,L1,L2,D) float32, zeroed; receives sum over key blocks of dS K
@@ -68,10 +68,17 @@ int launch_bwd(const BwdArgs& a, cudaStream_t stream);
 int bwd_rows_per_cta(int D);
 int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms);
 
-// delta[row] = sum_d (O[row,d] + R[row,d]) * dO[row,d]; `o_resid` (R, strides of O) may be nullptr
+// delta[(b,h,i), j] = sum_d (O[.,d] + R[.,d]) * dO[.,d]; `o_resid` (R, strides of O) may be nullptr;
+// `delta_pitch` = elements between rows (b,h,i) of delta (L2 rounded up to 128)
 int launch_preprocess(const void* o, const void* o_resid, const long long so[4], const void* dout,
-                      const long long sdo[4], float* delta, int B, int H, int L1, int L2, int D, bool bf16,
-                      cudaStream_t stream);
+                      const long long sdo[4], float* delta, int delta_pitch, int B, int H, int L1, int L2, int D,
+                      bool bf16, cudaStream_t stream);
+
+// out[b][h][q][k], (B, H, L2p, L2p) contiguous: the bias where q, k < L2 and the key is kept by
+// `key_mask` ((B, L2) bytes, non-zero = keep; nullptr = keep all), -inf for every other key, 0 for
+// the kept keys of the padding queries q >= L2
+int launch_mask_bias(const void* bias, const long long sb[4], const uint8_t* key_mask, void* out, int B, int H, int L2,
+                     int L2p, bool bf16, cudaStream_t stream);
 
 // Backward prologue, one launch: bias_t[bh][k][q] = bias[b][h][q][k] (16-bit elements; `sb` = element
 // strides of the bias) and zero-fill of the float32 dQ accumulator (`dq_elems` floats, a multiple of 4)

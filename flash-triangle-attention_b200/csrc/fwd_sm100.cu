@@ -75,7 +75,8 @@ struct FwdParams {
   int H, L1, L2;
   long long so_b, so_h, so_i, so_j;  // element strides of O (D stride is 1)
   float scale;                       // sm_scale
-  long long stat_stride;             // elements between the two statistics planes
+  int stat_pitch;                    // row pitch of the statistics: L2 rounded up to 128
+  long long stat_stride;             // elements between the statistics planes
 };
 
 template <int N>
@@ -114,7 +115,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x, bh = blockIdx.z;
   const int b = bh / p.H, h = bh % p.H;
-  const int nkb = p.L2 / 128;
+  const int nkb = (p.L2 + 127) / 128;  // a ragged last key block is padded by the loads (zeros) and masked by the bias (-inf)
   // This CTA walks the row groups blockIdx.y, blockIdx.y + gridDim.y, ... ("units") back to back;
   // loads and MMAs of the next unit start while the softmax warps finish the current one.
   const int ngroups = (p.L1 + G - 1) / G;
@@ -439,8 +440,11 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after_sync();
           const int i = i0 + g;
-          const float inv = 1.0f / l_new;
+          // a row whose every key is masked has an empty sum: O = 0 and statistics that make the
+          // backward pass recompute P = 0
+          const float inv = l_new > 0.f ? 1.0f / l_new : 0.f;
           const int j = jb * 128 + row;
+          const bool live = i < p.L1 && j < p.L2;  // padding rows of a short group / a ragged query block
           const long long ooff = b * p.so_b + h * p.so_h + static_cast<long long>(i) * p.so_i +
                                  static_cast<long long>(j) * p.so_j;
           uint16_t* optr = reinterpret_cast<uint16_t*>(p.o) + ooff;
@@ -452,7 +456,7 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             uint32_t orr[32];
             tmem_ld32(tbase + C::TMEM_O + g * kD + c * 32 + lane_off, orr);
             tmem_ld_wait();
-            if (i < p.L1) {
+            if (live) {
 #pragma unroll
               for (int v4 = 0; v4 < 4; ++v4) {
                 uint4 ov;
@@ -477,17 +481,21 @@ fta_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
           }
           if (i < p.L1) {
+            float m_safe_out = m_safe;
             // softmax statistics for the backward pass: -max (natural-log units) and -log2(sum).
             // Kept apart: their sum in one float would lose log2(sum) when |max| is huge.
-            const long long ridx = (static_cast<long long>(bh) * p.L1 + i) * p.L2 + j;
-            const float nl = -log2f(l_new);
-            p.lse[ridx] = -m_safe;
+            // (queries past L2 in a ragged block get 0 / -inf / -inf: whatever their logits, P = 0)
+            const long long ridx = (static_cast<long long>(bh) * p.L1 + i) * p.stat_pitch + j;
+            const bool empty = !(l_new > 0.f) || j >= p.L2;
+            const float nl = empty ? -INFINITY : -log2f(l_new);
+            if (j >= p.L2) m_safe_out = 0.f;
+            p.lse[ridx] = -m_safe_out;
             p.lse[p.stat_stride + ridx] = nl;
             // plane 2: both in one number, c = -(max*log2e + log2 sum), for rows where that loses
             // nothing; NaN marks rows whose max is so large (fully masked rows) that the
             // backward pass must use the two parts separately
             p.lse[2 * p.stat_stride + ridx] =
-                (fabsf(m_safe) > 1.0e4f) ? __int_as_float(0x7fc00000) : fmaf(-m_safe, kLog2e, nl);
+                (fabsf(m_safe_out) > 1.0e4f) ? __int_as_float(0x7fc00000) : fmaf(-m_safe_out, kLog2e, nl);
           }
         }
       }
@@ -521,13 +529,14 @@ int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
   p.so_i = a.so[2];
   p.so_j = a.so[3];
   p.scale = a.sm_scale;
-  p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * a.L2;
+  p.stat_pitch = (a.L2 + 127) / 128 * 128;
+  p.stat_stride = static_cast<long long>(a.B) * a.H * a.L1 * p.stat_pitch;
   // Row groups are dealt round-robin to grid.y CTAs per (query block, head). Pick the smallest
   // grid.y whose schedule (waves of one CTA per SM, the longest CTA setting the pace) is within
   // 3 % of the best: few long-lived CTAs amortise their start-up and keep the pipeline full
   // across row groups.
   const int ngroups = (a.L1 + C::G - 1) / C::G;
-  const long long per = static_cast<long long>(a.L2 / 128) * a.B * a.H;
+  const long long per = static_cast<long long>((a.L2 + 127) / 128) * a.B * a.H;
   int sms = 148;
   {
     int dev = 0;
@@ -556,7 +565,7 @@ int launch_fwd_t(const FwdArgs& a, cudaStream_t stream) {
       }
     }
   }
-  dim3 grid(a.L2 / 128, best_gy, a.B * a.H);
+  dim3 grid((a.L2 + 127) / 128, best_gy, a.B * a.H);
   kern<<<grid, 384, C::SMEM_BYTES, stream>>>(a.tmQ, a.tmK, a.tmV, a.tmBias, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -74,8 +74,8 @@ template <int kD, bool kBf16, bool kDense, bool kResid>
 __global__ void __launch_bounds__(256) preprocess_kernel(const uint16_t* __restrict__ o,
                                                          const uint16_t* __restrict__ o_resid,
                                                          const uint16_t* __restrict__ dout,
-                                                         float* __restrict__ delta, long long rows,
-                                                         int H, int L1, int L2, long long so_b,
+                                                         float* __restrict__ delta, int delta_pitch,
+                                                         long long rows, int H, int L1, int L2, long long so_b,
                                                          long long so_h, long long so_i, long long so_j,
                                                          long long sd_b, long long sd_h, long long sd_i,
                                                          long long sd_j) {
@@ -106,7 +106,8 @@ __global__ void __launch_bounds__(256) preprocess_kernel(const uint16_t* __restr
     }
 #pragma unroll
     for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (part == 0 && row < rows) delta[row] = s;
+    // rows of delta are `delta_pitch` apart (L2 rounded up to 128; equal to L2 in the dense case)
+    if (part == 0 && row < rows) delta[delta_pitch == L2 ? row : (row / L2) * delta_pitch + row % L2] = s;
   }
 }
 
@@ -132,6 +133,43 @@ __global__ void __launch_bounds__(256) dbias_cast_kernel(const float* __restrict
     pk.x = pack2<kBf16>(a.x, a.y);
     pk.y = pack2<kBf16>(a.z, a.w);
     reinterpret_cast<uint2*>(dst)[2 * nvec] = pk;
+  }
+}
+
+// Padded, masked copy of the pair bias for problems whose L2 is not a multiple of 128 and / or that
+// drop keys with a boolean mask: out (B*H, L2p, L2p), 8 elements (16 bytes) per thread.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) mask_bias_kernel(const uint16_t* __restrict__ bias, long long s_b, long long s_h,
+                                                        long long s_q, const uint8_t* __restrict__ key_mask,
+                                                        uint16_t* __restrict__ out, int BH, int H, int L2, int L2p) {
+  constexpr uint32_t NEG_INF = kBf16 ? 0xFF80u : 0xFC00u;
+  const int vec_per_row = L2p / 8;
+  const long long total = static_cast<long long>(BH) * L2p * vec_per_row;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int k8 = static_cast<int>(idx % vec_per_row) * 8;
+    const long long rq = idx / vec_per_row;
+    const int q = static_cast<int>(rq % L2p);
+    const int bh = static_cast<int>(rq / L2p);
+    const int b = bh / H, h = bh % H;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    if (k8 >= L2) {
+      w[0] = w[1] = w[2] = w[3] = NEG_INF | (NEG_INF << 16);  // padding keys: never attended
+    } else {
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);  // padding queries see a zero bias on the real keys
+      if (q < L2) v = __ldg(reinterpret_cast<const uint4*>(bias + b * s_b + h * s_h + q * s_q + k8));
+      const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+      uint2 m = make_uint2(0x01010101u, 0x01010101u);
+      if (key_mask) m = __ldg(reinterpret_cast<const uint2*>(key_mask + static_cast<long long>(b) * L2 + k8));
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t mm = (e < 2 ? m.x : m.y) >> ((e & 1) * 16);
+        const uint32_t lo = (mm & 0xffu) ? (vw[e] & 0xffffu) : NEG_INF;
+        const uint32_t hi = (mm & 0xff00u) ? (vw[e] >> 16) : NEG_INF;
+        w[e] = lo | (hi << 16);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + (static_cast<long long>(bh) * L2p + q) * L2p + k8) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -230,7 +268,7 @@ __global__ void __launch_bounds__(256) bwd_epilogue_kernel(const float* __restri
     }
     return;
   }
-  const int tiles = L2 / 64;
+  const int tiles = (L2 + 63) / 64;  // L2 is a multiple of 8: an 8-key / 4-query vector is inside or outside as a whole
   int t = blockIdx.x - dq_blocks;
   const int q0 = (t % tiles) * 64;
   t /= tiles;
@@ -243,9 +281,11 @@ __global__ void __launch_bounds__(256) bwd_epilogue_kernel(const float* __restri
   float4 acc[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool q_in = q0 + qc < L2;
   for (int pl = 0; pl < nplanes; ++pl) {  // fixed order
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
+      if (!q_in || k0 + kr + 16 * i >= L2) continue;
       const float4 x = __ldg(reinterpret_cast<const float4*>(src + static_cast<long long>(pl) * plane_stride +
                                                              static_cast<long long>(16 * i) * L2));
       acc[i].x += x.x;
@@ -268,6 +308,7 @@ __global__ void __launch_bounds__(256) bwd_epilogue_kernel(const float* __restri
   for (int it = 0; it < 2; ++it) {
     const int c = threadIdx.x + it * 256;
     const int q = c >> 3, k8 = (c & 7) * 8;
+    if (q0 + q >= L2 || k0 + k8 >= L2) continue;
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = tile[k8 + e][q];
@@ -310,8 +351,8 @@ bool is_dense(const long long s4[4], int H, int L1, int L2, int D) {
 }  // namespace
 
 int launch_preprocess(const void* o, const void* o_resid, const long long so[4], const void* dout,
-                      const long long sdo[4], float* delta, int B, int H, int L1, int L2, int D, bool bf16,
-                      cudaStream_t stream) {
+                      const long long sdo[4], float* delta, int delta_pitch, int B, int H, int L1, int L2, int D,
+                      bool bf16, cudaStream_t stream) {
   const long long rows = static_cast<long long>(B) * H * L1 * L2;
   const int grid = grid_for(rows * (D / 8), 256);
   const uint16_t* op = static_cast<const uint16_t*>(o);
@@ -319,8 +360,8 @@ int launch_preprocess(const void* o, const void* o_resid, const long long so[4],
   const uint16_t* dp = static_cast<const uint16_t*>(dout);
   const bool dense = is_dense(so, H, L1, L2, D) && is_dense(sdo, H, L1, L2, D);
   auto go = [&](auto kern) {
-    kern<<<grid, 256, 0, stream>>>(op, rp, dp, delta, rows, H, L1, L2, so[0], so[1], so[2], so[3], sdo[0], sdo[1],
-                                   sdo[2], sdo[3]);
+    kern<<<grid, 256, 0, stream>>>(op, rp, dp, delta, delta_pitch, rows, H, L1, L2, so[0], so[1], so[2], so[3],
+                                   sdo[0], sdo[1], sdo[2], sdo[3]);
   };
   auto pick = [&](auto d_tag, auto bf_tag) {
     constexpr int DD = decltype(d_tag)::value;
@@ -343,6 +384,18 @@ int launch_preprocess(const void* o, const void* o_resid, const long long so[4],
   return static_cast<int>(cudaGetLastError());
 }
 
+int launch_mask_bias(const void* bias, const long long sb[4], const uint8_t* key_mask, void* out, int B, int H, int L2,
+                     int L2p, bool bf16, cudaStream_t stream) {
+  const int grid = grid_for(static_cast<long long>(B) * H * L2p * (L2p / 8), 256);
+  if (bf16)
+    mask_bias_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(bias), sb[0], sb[1], sb[2], key_mask,
+                                                     static_cast<uint16_t*>(out), B * H, H, L2, L2p);
+  else
+    mask_bias_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(bias), sb[0], sb[1], sb[2], key_mask,
+                                                      static_cast<uint16_t*>(out), B * H, H, L2, L2p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int launch_bwd_prologue(const void* bias, const long long sb[4], void* bias_t, int B, int H, int L2, float* dq32,
                         long long dq_elems, cudaStream_t stream) {
   const int sms = num_sms();
@@ -360,7 +413,7 @@ int launch_bwd_epilogue(const float* dq32, void* dq, const long long sdq[4], int
                         cudaStream_t stream) {
   const long long rows = static_cast<long long>(B) * H * L1 * L2;
   const int dq_blocks = grid_for(rows * (D / 8), 256);
-  const int db_blocks = (L2 / 64) * (L2 / 64) * B * H;
+  const int db_blocks = ((L2 + 63) / 64) * ((L2 + 63) / 64) * B * H;
   const int grid = dq_blocks + db_blocks;
   uint16_t* out = static_cast<uint16_t*>(dq);
   uint16_t* cast = static_cast<uint16_t*>(dbias_cast);

@@ -11,8 +11,10 @@ Triton launches replaced by hand-written sm_100a kernels reached through the C A
 
 Differences from the reference, all relaxations:
   * fp16 and bf16 (the reference is fp16 only, line 99); L1 may differ from L2 (the reference
-    needs a square pair representation, lines 584 and 616); L2 must be a multiple of 128 but
-    need not be a power of two (line 618);
+    needs a square pair representation, lines 584 and 616); L2 need not be a power of two
+    (line 618) nor a multiple of 128 (ragged last blocks are padded by the tile loads and clipped
+    by the stores; only a bias-sized tensor is staged, ``fta_mask_bias``); a boolean ``key_mask``
+    removes keys;
   * ``dO`` and non-dense inputs are made contiguous instead of asserted on (604-606);
   * dBias is accumulated in float32 in a fixed order (bit-reproducible) and rounded once,
     instead of fp16 atomics (425-426); with bf16 inputs the forward also saves the 16 bits of O
@@ -105,9 +107,13 @@ def _problem(q: torch.Tensor) -> FtaProblem:
     return FtaProblem(B, H, L1, L2, D, _cabi.FTA_BF16 if q.dtype == torch.bfloat16 else _cabi.FTA_FP16)
 
 
+def _l2p(L2: int) -> int:
+    return (L2 + 127) // 128 * 128
+
+
 class _attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, b_pw, sm_scale, group=None):
+    def forward(ctx, q, k, v, b_pw, sm_scale, group=None, key_mask=None):
         HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
         assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
         assert HEAD_DIM_K in {32, 64}, "head dimension must be 32 or 64"
@@ -117,43 +123,57 @@ class _attention(torch.autograd.Function):
         assert q.dim() == 5 and q.shape == k.shape == v.shape
         B, H, L1, L2, D = q.shape
         assert b_pw.shape == (B, H, L2, L2), "bias must be (B, H, L2, L2)"
-        assert L2 % 128 == 0, "L2 must be a multiple of 128"
+        assert L2 % 8 == 0, "the kernels address rows of L2 elements with 16-byte steps (attention() pads other L2)"
 
         st = _status_of(q.device)
         st.raise_if_set()  # an earlier call's device-side failure, seen through the host mirror
         q, k, v, b_pw = _dense(q), _dense(k), _dense(v), _dense(b_pw)
+        L2p = _l2p(L2)
+        L = _cabi.lib()
+        prob = _problem(q)
         o = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=q.device)
-        lse = torch.empty((3, B, H, L1, L2), dtype=torch.float32, device=q.device)  # softmax statistics
+        lse = torch.empty((3, B, H, L1, L2p), dtype=torch.float32, device=q.device)  # softmax statistics
         # the bits of O that rounding to bf16 drops, for the backward's delta (fp16 keeps enough)
         need_bwd = any(ctx.needs_input_grad[:4])
         o_res = torch.empty_like(o) if (need_bwd and _SAVE_O_RESIDUAL and q.dtype == torch.bfloat16) else None
-        prob = _problem(q)
         with torch.cuda.device(q.device):
             stream = torch.cuda.current_stream().cuda_stream
-            check(_cabi.lib().fta_forward(prob, t5(q), t5(k), t5(v), t4(b_pw), float(sm_scale), t5(o),
-                                          None if o_res is None else o_res.data_ptr(),
-                                          lse.data_ptr(), st.word.data_ptr(), stream), "fta_forward")
+            bias_k = b_pw  # what the kernels read
+            if key_mask is not None or L2p != L2:
+                # Ragged L2 and / or a boolean key mask: only this bias-sized tensor is staged (whole
+                # 128-blocks, -inf on padding and masked keys); q, k, v are read in place.
+                km = None
+                if key_mask is not None:
+                    assert key_mask.dtype == torch.bool and key_mask.shape == (B, L2), "key_mask: bool (B, L2)"
+                    km = key_mask.to(device=q.device, dtype=torch.uint8).contiguous()
+                bias_k = torch.empty((B, H, L2p, L2p), dtype=q.dtype, device=q.device)
+                check(L.fta_mask_bias(prob, t4(b_pw), None if km is None else km.data_ptr(), bias_k.data_ptr(), stream),
+                      "fta_mask_bias")
+            check(L.fta_forward(prob, t5(q), t5(k), t5(v), t4(bias_k), float(sm_scale), t5(o),
+                                None if o_res is None else o_res.data_ptr(),
+                                lse.data_ptr(), st.word.data_ptr(), stream), "fta_forward")
             st.publish()
         if _DEBUG:
             check_device_status(q.device)
-        ctx.save_for_backward(q, k, v, o, b_pw, lse, o_res)
+        ctx.save_for_backward(q, k, v, o, bias_k, lse, o_res)
         ctx.sm_scale = float(sm_scale)
         ctx.group = group
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, o, b_pw, lse, o_res = ctx.saved_tensors
+        q, k, v, o, bias_k, lse, o_res = ctx.saved_tensors
         assert do.dtype == q.dtype
         do = _dense(do)
         B, H, L1, L2, D = q.shape
+        L2p = _l2p(L2)
         dev = q.device
         dq = torch.empty((B, H, L1, L2, D), dtype=q.dtype, device=dev)
         dk = torch.empty_like(dq)
         dv = torch.empty_like(dq)
-        db = torch.empty((B, H, L2, L2), dtype=b_pw.dtype, device=dev)
+        db = torch.empty((B, H, L2, L2), dtype=q.dtype, device=dev)
         db32 = torch.empty((B, H, L2, L2), dtype=torch.float32, device=dev)
-        delta = torch.empty((B, H, L1, L2), dtype=torch.float32, device=dev)
+        delta = torch.empty((B, H, L1, L2p), dtype=torch.float32, device=dev)
         prob = _problem(q)
         L = _cabi.lib()
         ws_bytes = int(L.fta_bwd_workspace_bytes(prob))
@@ -166,7 +186,7 @@ class _attention(torch.autograd.Function):
             stream = torch.cuda.current_stream().cuda_stream
             check(L.fta_bwd_preprocess(prob, t5(o), None if o_res is None else o_res.data_ptr(), t5(do),
                                        delta.data_ptr(), stream), "fta_bwd_preprocess")
-            check(L.fta_backward(prob, t5(q), t5(k), t5(v), t4(b_pw), t5(do), lse.data_ptr(), delta.data_ptr(),
+            check(L.fta_backward(prob, t5(q), t5(k), t5(v), t4(bias_k), t5(do), lse.data_ptr(), delta.data_ptr(),
                                  ctx.sm_scale, t5(dq), t5(dk), t5(dv), db32.data_ptr(),
                                  None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
                                  status.data_ptr(), stream), "fta_backward")
@@ -179,7 +199,7 @@ class _attention(torch.autograd.Function):
         if _DEBUG:
             check_device_status(dev)
         _last["dbias_f32"] = db32
-        return dq, dk, dv, db, None, None
+        return dq, dk, dv, db, None, None, None
 
 
 def attention(q, k, v, b_pw, sm_scale, group=None, key_mask=None):
@@ -187,41 +207,28 @@ def attention(q, k, v, b_pw, sm_scale, group=None, key_mask=None):
     (B, H, L1, L2, D) and a pair bias (B, H, L2, L2) shared by the L1 rows; differentiable in
     q, k, v and b_pw (dBias is summed over L1). See the module docstring.
 
-    Two extensions of the reference's call (flash_tt_attn.py:663), both keyword-only in spirit:
-    ``key_mask`` (bool, broadcastable to (B, 1, 1, L2) or of shape (B, L2); True = attend) removes
-    keys without the caller building a -1e9 bias, and ``L2`` need not be a multiple of 128.
-    Either one goes through a padded copy of the inputs (L2 rounded up to 128, padded / masked
-    keys get a large negative bias, padded queries are cropped from the result and receive zero
-    gradient); the kernels themselves always see whole 128-key tiles."""
-    L2 = q.shape[3]
-    if key_mask is None and L2 % 128 == 0:
-        return _attention.apply(q, k, v, b_pw, sm_scale, group)
-    return _attention_padded(q, k, v, b_pw, sm_scale, group, key_mask)
-
-
-def _attention_padded(q, k, v, b_pw, sm_scale, group, key_mask):
+    Two extensions of the reference's call (flash_tt_attn.py:663; its README lists both as to-do,
+    README.md:17-18): ``key_mask`` (bool (B, L2), or anything that broadcasts to (B, 1, 1, L2);
+    True = attend) removes keys, and ``L2`` need not be a multiple of 128. Both are handled inside
+    the kernels - ragged last blocks are padded by the tile loads and clipped by the stores, masked
+    keys get exactly zero probability and exactly zero dBias, dK, dV - and only a bias-sized tensor
+    is staged; q, k, v are never copied. (An ``L2`` that is not a multiple of 8 is first padded to
+    one: the kernels step through rows of ``L2`` elements 16 bytes at a time.) A query whose every
+    key is masked gets a zero output row and zero gradients."""
     B, H, L1, L2, D = q.shape
-    Lp = (L2 + 127) // 128 * 128
-    pad = Lp - L2
-    # the most negative bias that is still finite in the bias dtype and keeps exp2 at exactly 0
-    neg = -6.0e4 if b_pw.dtype == torch.float16 else -1.0e9
-    bias = b_pw
     if key_mask is not None:
-        km = key_mask
-        if km.dim() == 2:
-            km = km[:, None, None, :]
-        assert km.dtype == torch.bool and km.shape[-1] == L2
-        bias = torch.where(km.expand(B, H, L2, L2) if km.dim() == 4 else km, bias,
-                           torch.full((), neg, dtype=bias.dtype, device=bias.device))
-    if pad:
-        # F.pad is differentiable: gradients of the padded parts are dropped on the way back
-        F = torch.nn.functional
-        q = F.pad(q, (0, 0, 0, pad))
-        k = F.pad(k, (0, 0, 0, pad))
-        v = F.pad(v, (0, 0, 0, pad))
-        bias = F.pad(bias, (0, pad, 0, pad), value=neg)
-    out = _attention.apply(q, k, v, bias, sm_scale, group)
-    return out[:, :, :, :L2] if pad else out
+        if key_mask.dim() == 4:
+            key_mask = key_mask.reshape(key_mask.shape[0], L2)
+        key_mask = key_mask.expand(B, L2)
+    if L2 % 8 == 0:
+        return _attention.apply(q, k, v, b_pw, sm_scale, group, key_mask)
+    pad = (L2 + 7) // 8 * 8 - L2
+    F = torch.nn.functional  # F.pad is differentiable: gradients of the padding are dropped on the way back
+    if key_mask is None:
+        key_mask = torch.ones((B, L2), dtype=torch.bool, device=q.device)
+    out = _attention.apply(F.pad(q, (0, 0, 0, pad)), F.pad(k, (0, 0, 0, pad)), F.pad(v, (0, 0, 0, pad)),
+                           F.pad(b_pw, (0, pad, 0, pad)), sm_scale, group, F.pad(key_mask, (0, pad), value=False))
+    return out[:, :, :, :L2]
 
 
 def reference_tt_attn(q, k, v, b, sm_scale):
@@ -258,90 +265,91 @@ def shard_rows(L1: int, rank: int, world: int) -> slice:
     return slice(min(L1, rank * per), min(L1, (rank + 1) * per))
 
 
+def _block_sizes(L1: int, block_rows: int):
+    """Blocks of L1 rows for the streamed entry point: full blocks in the middle, a third and two
+    thirds of a block at either end, so that the first copy in and the last copy out (which nothing
+    overlaps) are short."""
+    ramp = [max(1, block_rows // 3), max(1, 2 * block_rows // 3)]
+    if L1 <= 3 * block_rows:
+        return [block_rows] * (L1 // block_rows) + ([L1 % block_rows] if L1 % block_rows else [])
+    left = L1 - 2 * sum(ramp)
+    sizes = ramp + [block_rows] * (left // block_rows)
+    if left % block_rows:
+        sizes.append(left % block_rows)
+    return sizes + ramp[::-1]
+
+
+def _copy_rows(lib, dst, dst_row0, src, src_row0, nrows, stream):
+    """Rows [row0, row0 + nrows) of the L1 axis of every (b, h): one strided transfer. Both tensors
+    are (B, H, *, L2, D) and dense in their last two axes and across (b, h)."""
+    B, H = dst.shape[0], dst.shape[1]
+    es = dst.element_size()
+    row = dst.shape[3] * dst.shape[4] * es
+    assert dst.stride(0) == H * dst.stride(1) and src.stride(0) == H * src.stride(1)
+    assert dst.stride(2) * es == row and src.stride(2) * es == row
+    check(lib.fta_memcpy_2d(dst.data_ptr() + dst_row0 * row, dst.stride(1) * es, src.data_ptr() + src_row0 * row,
+                            src.stride(1) * es, nrows * row, B * H, stream), "fta_memcpy_2d")
+
+
 def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, group=None):
     """Forward + backward for tensors that live in (pinned) HOST memory, streamed through the GPU
     in blocks of L1 rows: the copies of block i+1 (host to device) and of the results of block
     i-1 (device to host) run on their own streams while the kernels of block i run, so a call
     costs about max(copy in, copy out, compute) instead of their sum. Rows of L1 are independent
     problems; only dBias couples them, and it is summed over the blocks in float32, in block
-    order, and rounded once.
+    order, and rounded once. Each block moves with one strided transfer per tensor
+    (``fta_memcpy_2d``) through three device slots.
 
     host : dict with ``q, k, v, do`` of shape (B, H, L1, L2, D) and ``bias`` (B, H, L2, L2), CPU
-           tensors (pinned for asynchronous copies), 16-bit dtype
+           tensors (pinned for asynchronous copies), contiguous, 16-bit dtype
     out  : dict with ``o, dq, dk, dv`` like ``q`` and ``dbias`` like ``bias``, CPU tensors (pinned)
     group: with a process group, ``host`` holds this rank's rows and dBias is all-reduced once.
     Returns after everything has arrived in ``out``.
     """
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    q_h, k_h, v_h, do_h, b_h = host["q"], host["k"], host["v"], host["do"], host["bias"]
+    q_h, b_h = host["q"], host["bias"]
     B, H, L1, L2, D = q_h.shape
-    cur = torch.cuda.current_stream(dev)
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    # Block boundaries: full blocks in the middle, a third and two thirds of a block at either end, so
-    # that the first copy in and the last copy out (which nothing overlaps) are short.
-    ramp = [max(1, block_rows // 3), max(1, 2 * block_rows // 3)]
-    sizes = []
-    left = L1
-    if L1 > 3 * block_rows:
-        sizes += ramp
-        left -= 2 * sum(ramp)
-        sizes += [block_rows] * (left // block_rows)
-        if left % block_rows:
-            sizes.append(left % block_rows)
-        sizes += ramp[::-1]
-    else:
-        sizes = [block_rows] * (L1 // block_rows) + ([L1 % block_rows] if L1 % block_rows else [])
-    bounds = [0]
-    for sz in sizes:
-        bounds.append(bounds[-1] + sz)
-    assert bounds[-1] == L1
-    nblk = len(sizes)
-    bufs = [{k: torch.empty((B, H, min(block_rows, L1), L2, D), dtype=q_h.dtype, device=dev)
-             for k in ("q", "k", "v", "do")} for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_comp = [torch.cuda.Event() for _ in range(2)]
-    s_in.wait_stream(cur)
-    with torch.cuda.stream(s_in):
-        bias = b_h.to(dev, non_blocking=True)
-    db32 = torch.zeros((B, H, L2, L2), dtype=torch.float32, device=dev)
-    keep = []  # results in flight to the host
-
-    def copy_rows(dst, src, r0, r1):
-        # per (b, h) the block of rows is contiguous on both sides: plain asynchronous copies
-        for b_ in range(B):
-            for h_ in range(H):
-                dst[b_, h_, : r1 - r0].copy_(src[b_, h_, r0:r1], non_blocking=True)
-
-    for blk in range(nblk):
-        slot = blk & 1
-        r0, r1 = bounds[blk], bounds[blk + 1]
+    L = _cabi.lib()
+    NSLOT = 3
+    names_in, names_out = ("q", "k", "v", "do"), ("o", "dq", "dk", "dv")
+    for t in [host[n] for n in names_in] + [out[n] for n in names_out]:
+        assert t.is_contiguous() and t.shape == q_h.shape and t.dtype == q_h.dtype
+    with torch.cuda.device(dev):
+        cur = torch.cuda.current_stream(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        sizes = _block_sizes(L1, block_rows)
+        cap = max(sizes)
+        bufs = [{k: torch.empty((B, H, cap, L2, D), dtype=q_h.dtype, device=dev) for k in names_in}
+                for _ in range(NSLOT)]
+        ev_in = [torch.cuda.Event() for _ in range(NSLOT)]
+        ev_comp = [torch.cuda.Event() for _ in range(NSLOT)]
+        s_in.wait_stream(cur)
         with torch.cuda.stream(s_in):
-            if blk >= 2:
-                s_in.wait_event(ev_comp[slot])  # the kernels of block blk-2 have read this slot
-            for name, src in (("q", q_h), ("k", k_h), ("v", v_h), ("do", do_h)):
-                copy_rows(bufs[slot][name], src, r0, r1)
+            bias = b_h.to(dev, non_blocking=True)
+        db32 = torch.zeros((B, H, L2, L2), dtype=torch.float32, device=dev)
+        r0 = 0
+        for blk, n in enumerate(sizes):
+            slot = blk % NSLOT
+            if blk >= NSLOT:
+                s_in.wait_event(ev_comp[slot])  # the kernels of block blk - NSLOT have read this slot
+            for name in names_in:
+                _copy_rows(L, bufs[slot][name], 0, host[name], r0, n, s_in.cuda_stream)
             ev_in[slot].record(s_in)
-        cur.wait_event(ev_in[slot])
-        n = r1 - r0
-        qd, kd, vd = (bufs[slot][name][:, :, :n].detach().requires_grad_() for name in ("q", "k", "v"))
-        bias_leaf = bias.detach().requires_grad_()
-        o = _attention.apply(qd, kd, vd, bias_leaf, sm_scale, None)
-        o.backward(bufs[slot]["do"][:, :, :n])
-        db32 += _last["dbias_f32"]
-        ev_comp[slot].record(cur)
-        res = {"o": o.detach(), "dq": qd.grad, "dk": kd.grad, "dv": vd.grad}
-        with torch.cuda.stream(s_out):
+            cur.wait_event(ev_in[slot])
+            qd, kd, vd = (bufs[slot][name][:, :, :n].detach().requires_grad_() for name in ("q", "k", "v"))
+            o = _attention.apply(qd, kd, vd, bias.detach().requires_grad_(), sm_scale, None, None)
+            o.backward(bufs[slot]["do"][:, :, :n])
+            db32 += _last["dbias_f32"]
+            ev_comp[slot].record(cur)
             s_out.wait_event(ev_comp[slot])
-            for name, t in res.items():
-                t.record_stream(s_out)
-                for b_ in range(B):
-                    for h_ in range(H):
-                        out[name][b_, h_, r0:r1].copy_(t[b_, h_], non_blocking=True)
-        keep.append(res)
-    if group is not None:
-        torch.distributed.all_reduce(db32, op=torch.distributed.ReduceOp.SUM, group=group)
-    out["dbias"].copy_(db32.to(b_h.dtype), non_blocking=True)
-    _last["dbias_f32"] = db32
-    cur.wait_stream(s_out)
-    torch.cuda.synchronize(dev)
+            for name, t in (("o", o.detach()), ("dq", qd.grad), ("dk", kd.grad), ("dv", vd.grad)):
+                t.record_stream(s_out)  # results are dense (B, H, n, L2, D) tensors of this block
+                _copy_rows(L, out[name], r0, t, 0, n, s_out.cuda_stream)
+            r0 += n
+        if group is not None:
+            torch.distributed.all_reduce(db32, op=torch.distributed.ReduceOp.SUM, group=group)
+        out["dbias"].copy_(db32.to(b_h.dtype), non_blocking=True)
+        _last["dbias_f32"] = db32
+        cur.wait_stream(s_out)
+        torch.cuda.synchronize(dev)
     check_device_status(dev)

@@ -20,8 +20,12 @@
  *  - device-side waits are bounded; a wait that runs out writes a non-zero code to the
  *    caller's status word (see fta_read_status) and the kernel returns;
  *  - supported: dtype fp16 / bf16 (q, k, v, bias, o, dO and the gradients share it),
- *    D in {32, 64}, L2 a multiple of 128, any L1 >= 1 (L1 != L2 is fine: a shard of rows),
- *    innermost (D) stride 1 and 16-byte aligned rows;
+ *    D in {32, 64}, any L1 >= 1 (L1 != L2 is fine: a shard of rows), innermost (D) stride 1 and
+ *    16-byte aligned rows; L2 a multiple of 128, or any multiple of 8 with the bias passed
+ *    through fta_mask_bias first (ragged last blocks are padded on the fly by the loads and
+ *    clipped by the stores: q, k, v, dO and the outputs are never copied);
+ *  - L2p below is L2 rounded up to a multiple of 128; the softmax statistics and delta have rows
+ *    of L2p floats (the kernels move them in whole 128-query blocks);
  *  - every device pointer handed to the library (tensors, lse, delta, dBias buffers, the optional
  *    residual) must be 16-byte aligned, the workspace 256-byte aligned: FTA_ERR_ALIGN /
  *    FTA_ERR_WORKSPACE otherwise (the kernels move data with 16-byte vectors and bulk copies).
@@ -47,7 +51,7 @@ enum { FTA_FP16 = 0, FTA_BF16 = 1 };
 enum {
   FTA_OK = 0,
   FTA_ERR_NULL = -1,       /* a required pointer is NULL */
-  FTA_ERR_SHAPE = -2,      /* non-positive size, or L2 not a multiple of 128 */
+  FTA_ERR_SHAPE = -2,      /* non-positive size, or L2 not a multiple of 8 */
   FTA_ERR_HEAD_DIM = -3,   /* D not in {32, 64} */
   FTA_ERR_DTYPE = -4,      /* dtype not FTA_FP16 / FTA_BF16 */
   FTA_ERR_STRIDE = -5,     /* D stride != 1, or a stride that is not a multiple of 8 elements */
@@ -88,7 +92,7 @@ FTA_API int fta_last_cuda_error(void);
 /* Forward pass. Replaces the `_attn_fwd` launch of `_attention.forward`
  * (flash_tt_attn.py:556-593, kernel 128-264): writes O (same dtype as q) and the softmax
  * statistics of every query row for the backward pass, `lse`, float32 contiguous of shape
- * (3,B,H,L1,L2): plane 0 holds -max_k(S) in natural-log units, plane 1 holds
+ * (3,B,H,L1,L2p): plane 0 holds -max_k(S) in natural-log units, plane 1 holds
  * -log2(sum_k exp(S - max)). The reference saves their combination, the base-2
  * log-sum-exp max*log2(e) + log2(sum) (flash_tt_attn.py:258-263) = -(plane0*log2(e) + plane1);
  * the two parts are kept apart here because their float32 sum loses log2(sum) when a row is
@@ -100,17 +104,34 @@ FTA_API int fta_last_cuda_error(void);
  * to fta_bwd_preprocess it makes delta = rowsum(dO * O) as if O had 16 mantissa bits; with bf16
  * and O rounded to 8 bits the error of delta alone costs about 0.01 max-abs in a dBias summed
  * over several hundred rows. The reference has no such output (it is fp16 only).
+ * `bias` spans whole 128-blocks: the caller's (B,H,L2,L2) tensor when L2 is a multiple of 128,
+ * else the (B,H,L2p,L2p) copy made by fta_mask_bias (also the way to drop keys with a mask).
  * `status` points to one int32 the caller zeroed. */
 FTA_API int fta_forward(const FtaProblem* prob, const FtaTensor5* q, const FtaTensor5* k,
                 const FtaTensor5* v, const FtaTensor4* bias, float sm_scale,
                 const FtaTensor5* o, void* o_resid, float* lse, int32_t* status, void* stream);
 
 /* Backward preprocess. Replaces `_attn_bwd_preprocess` (flash_tt_attn.py:266-288, launched
- * at 636-641): delta[b,h,i,j] = sum_d O[b,h,i,j,d] * dO[b,h,i,j,d], float32 contiguous.
+ * at 636-641): delta[b,h,i,j] = sum_d O[b,h,i,j,d] * dO[b,h,i,j,d], float32, shape (B,H,L1,L2p)
+ * contiguous (entries j >= L2 are set to 0).
  * `o_resid` (may be NULL) is the residual fta_forward wrote, laid out like `o`: when given,
  * O + residual takes the place of O. */
 FTA_API int fta_bwd_preprocess(const FtaProblem* prob, const FtaTensor5* o, const void* o_resid,
                        const FtaTensor5* dout, float* delta, void* stream);
+
+/* Padded, masked copy of the pair bias, for problems whose L2 is not a multiple of 128 and / or
+ * that remove keys with a boolean mask (the reference's roadmap items, README.md:17-18; its
+ * kernels have neither). `out` is (B,H,L2p,L2p) contiguous in the bias dtype:
+ *     out[b,h,q,k] = bias[b,h,q,k]   for q, k < L2 and key_mask[b,k] != 0
+ *                  = -inf            for every other key k (masked, or padding k >= L2)
+ *                  = 0               for kept keys of the padding queries q >= L2
+ * `key_mask` is (B,L2) bytes on the device, 8-byte aligned, non-zero = attend; NULL keeps every
+ * key. Pass `out` as the bias (strides L2p*L2p*H, L2p*L2p, L2p, 1) to fta_forward and
+ * fta_backward: masked keys then get exactly zero probability and exactly zero dBias / dK / dV;
+ * a query whose every key is masked gets O = 0 and zero gradients. dBias is still returned
+ * as (B,H,L2,L2). Only this bias-sized tensor is staged; q, k, v, dO are read in place. */
+FTA_API int fta_mask_bias(const FtaProblem* prob, const FtaTensor4* bias, const uint8_t* key_mask, void* out,
+                          void* stream);
 
 /* Bytes of workspace fta_backward needs for `prob` (a float32 dQ accumulator and the
  * partial dBias planes). 256-byte aligned workspace required. */
@@ -162,6 +183,15 @@ FTA_API int fta_backward_noalloc(const FtaProblem* prob, const FtaTensor5* q, co
 
 /* Size in bytes of the fixed scratch array used by fta_backward_noalloc. */
 FTA_API size_t fta_noalloc_max_bytes(void);
+
+/* Strided block copy on `stream`: `rows` pieces of `width_bytes`, `src_pitch_bytes` apart in the
+ * source and `dst_pitch_bytes` apart in the destination (one cudaMemcpy2DAsync; either side may be
+ * pinned host or device memory, the direction is inferred from the pointers). What the host-memory
+ * entry point of the Python module uses to move a block of L1 rows of every (b,h) of a
+ * (B,H,L1,L2,D) tensor with ONE transfer per tensor instead of one per (b,h). It has no
+ * counterpart in the reference (whose tensors always live on the device). */
+FTA_API int fta_memcpy_2d(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes,
+                          size_t width_bytes, size_t rows, void* stream);
 
 /* Profiling hook, off by default. After this call, every fta_backward on the calling thread
  * records `start_event` right before and `stop_event` right after its main kernel (the

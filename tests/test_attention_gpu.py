@@ -283,31 +283,74 @@ def test_ending_node_views_need_no_copy_in_forward_and_backward():
 
 
 
-def test_key_mask_and_ragged_l2_through_padding():
-    """L2 = 200 (not a multiple of 128) with a boolean key mask: equal to the oracle on the same
-    problem written with a -1e9 bias; masked keys receive exactly zero dBias columns."""
-    B, H, L1, L2, D = 1, 2, 3, 200, 32
-    g = torch.Generator().manual_seed(7)
-    q, k, v, do = [torch.randn(B, H, L1, L2, D, generator=g).to(torch.bfloat16) for _ in range(4)]
-    bias = torch.randn(B, H, L2, L2, generator=g).to(torch.bfloat16)
-    mask = torch.rand(B, L2, generator=g) > 0.2
-    mask[:, 0] = True
+@pytest.mark.parametrize("L2,masked,dtype", [(200, True, "bf16"), (300, True, "bf16"), (392, False, "bf16"),
+                                             (136, True, "fp16"), (256, True, "bf16"), (200, False, "fp16")])
+def test_ragged_l2_and_key_mask_in_the_kernels(L2, masked, dtype, monkeypatch):
+    """L2 not a multiple of 128 and / or a boolean key mask, handled inside the kernels: q, k, v are
+    read in place (no padded copy: ``F.pad`` is forbidden here for L2 % 8 == 0), the results equal
+    the oracle on the same problem written with a -1e9 bias, masked keys receive exactly zero dBias,
+    dK and dV."""
+    B, H, L1, D = 2, 2, 5, 32
+    tdt = _dt(dtype)
+    g = torch.Generator().manual_seed(7 + L2)
+    q, k, v, do = [torch.randn(B, H, L1, L2, D, generator=g).to(tdt) for _ in range(4)]
+    bias = torch.randn(B, H, L2, L2, generator=g).to(tdt)
+    mask = None
+    if masked:
+        mask = torch.rand(B, L2, generator=g) > 0.2
+        mask[:, 0] = True
+    if L2 % 8 == 0:
+        def no_pad(*a, **kw):
+            raise AssertionError("attention() copied its inputs for an L2 the kernels handle natively")
+        monkeypatch.setattr(torch.nn.functional, "pad", no_pad)
     scale = D ** -0.5
     leaves = [a.cuda().requires_grad_(True) for a in (q, k, v, bias)]
-    o = fta.attention(*leaves, scale, key_mask=mask.cuda())
+    o = fta.attention(*leaves, scale, key_mask=None if mask is None else mask.cuda())
     o.backward(do.cuda())
     fta.check_device_status()
     assert o.shape == (B, H, L1, L2, D)
-    bm = torch.where(mask[:, None, None, :], bias.float(), torch.tensor(-1.0e9))
+    bm = bias.float()
+    if mask is not None:
+        bm = torch.where(mask[:, None, None, :], bm, torch.tensor(-1.0e9))
     ref = npo.forward_backward(q.float().numpy(), k.float().numpy(), v.float().numpy(), bm.numpy(),
                                do.float().numpy(), scale)
-    got = {"o": o, "dq": leaves[0].grad, "dk": leaves[1].grad, "dv": leaves[2].grad, "dbias": leaves[3].grad}
-    for name in ("o", "dq", "dk", "dv", "dbias"):
-        a = got[name].detach().float().cpu().numpy()
-        assert npo.max_abs(a, ref[name]) <= MAX_ABS, name
-        assert npo.rel_l2(a, ref[name]) <= REL_L2 * (2 if name == "dbias" else 1), name
-    dead = ~mask[0].numpy()
-    assert np.all(got["dbias"].float().cpu().numpy()[0][:, :, dead] == 0.0)
+    got = {"o": o, "dq": leaves[0].grad, "dk": leaves[1].grad, "dv": leaves[2].grad, "dbias": leaves[3].grad,
+           "dbias32": fta.last_dbias_f32()}
+    got = {n: t.detach().float().cpu().numpy() for n, t in got.items()}
+    got["dbias32"] = got["dbias32"][:, :, :L2, :L2]  # an L2 that is not a multiple of 8 ran padded to one
+    for name in ("o", "dq", "dk", "dv", "dbias32"):
+        want = ref["dbias" if name == "dbias32" else name]
+        assert not np.isnan(got[name]).any(), name
+        assert npo.max_abs(got[name], want) <= MAX_ABS, (name, npo.max_abs(got[name], want))
+        assert npo.rel_l2(got[name], want) <= REL_L2, name
+    assert npo.rel_l2(got["dbias"], ref["dbias"]) <= REL_L2
+    if mask is not None:
+        for b_ in range(B):
+            dead = ~mask[b_].numpy()
+            assert np.all(got["dbias32"][b_][:, :, dead] == 0.0)
+            assert np.all(got["dk"][b_][:, :, dead] == 0.0) and np.all(got["dv"][b_][:, :, dead] == 0.0)
+
+
+def test_fully_masked_batch_element_gives_zero_rows():
+    """Every key of a batch element masked: its output rows and all its gradients are exactly 0,
+    nothing is NaN, and the other batch element is untouched."""
+    B, H, L1, L2, D = 2, 1, 3, 128, 32
+    g = torch.Generator().manual_seed(3)
+    q, k, v, do = [torch.randn(B, H, L1, L2, D, generator=g).to(torch.bfloat16).cuda() for _ in range(4)]
+    bias = torch.randn(B, H, L2, L2, generator=g).to(torch.bfloat16).cuda()
+    mask = torch.ones(B, L2, dtype=torch.bool)
+    mask[1] = False
+    leaves = [a.requires_grad_(True) for a in (q, k, v, bias)]
+    o = fta.attention(*leaves, D ** -0.5, key_mask=mask.cuda())
+    o.backward(do)
+    fta.check_device_status()
+    for t in (o, *[l.grad for l in leaves]):
+        assert torch.isfinite(t).all()
+    assert float(o[1].abs().max()) == 0.0
+    for l in leaves:
+        assert float(l.grad[1].abs().max()) == 0.0
+    ref = fta.attention(q[:1].detach(), k[:1].detach(), v[:1].detach(), bias[:1].detach(), D ** -0.5)
+    assert torch.equal(ref, o[:1].detach())
 
 
 def test_streamed_host_entry_point_matches_the_device_path():
