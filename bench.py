@@ -49,7 +49,7 @@ METRIC = "fwd+bwd TFLOP/s, fused triangle attention B=1 H=4 L=768 D=32 bf16"
 # fraction of it.
 BWD_KERNEL_DRAM_BYTES = 1228830208 + 1208799488
 # L1 rows per block of the end-to-end leg (host tensors streamed through the GPU)
-E2E_BLOCK_ROWS = int(os.environ.get("FTA_E2E_BLOCK_ROWS", "128"))
+E2E_BLOCK_ROWS = int(os.environ.get("FTA_E2E_BLOCK_ROWS", "96"))
 
 
 def _peaks():

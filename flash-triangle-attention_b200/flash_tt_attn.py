@@ -285,7 +285,8 @@ def _copy_rows(lib, dst, dst_row0, src, src_row0, nrows, stream):
     B, H = dst.shape[0], dst.shape[1]
     es = dst.element_size()
     row = dst.shape[3] * dst.shape[4] * es
-    assert dst.stride(0) == H * dst.stride(1) and src.stride(0) == H * src.stride(1)
+    # one pitch for every (b, h) slab (the stride of a size-1 batch axis carries no meaning)
+    assert B == 1 or (dst.stride(0) == H * dst.stride(1) and src.stride(0) == H * src.stride(1))
     assert dst.stride(2) * es == row and src.stride(2) * es == row
     check(lib.fta_memcpy_2d(dst.data_ptr() + dst_row0 * row, dst.stride(1) * es, src.data_ptr() + src_row0 * row,
                             src.stride(1) * es, nrows * row, B * H, stream), "fta_memcpy_2d")
@@ -298,10 +299,12 @@ def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, 
     costs about max(copy in, copy out, compute) instead of their sum. Rows of L1 are independent
     problems; only dBias couples them, and it is summed over the blocks in float32, in block
     order, and rounded once. Each block moves with one strided transfer per tensor
-    (``fta_memcpy_2d``) through three device slots.
+    (``fta_memcpy_2d``) through three device slots, and its kernels are enqueued straight through
+    the C ABI on buffers allocated once per call (no autograd graph: a block costs the host a
+    fraction of a millisecond, which matters because a block's kernels run for about as long).
 
     host : dict with ``q, k, v, do`` of shape (B, H, L1, L2, D) and ``bias`` (B, H, L2, L2), CPU
-           tensors (pinned for asynchronous copies), contiguous, 16-bit dtype
+           tensors (pinned for asynchronous copies), contiguous, 16-bit dtype; L2 a multiple of 8
     out  : dict with ``o, dq, dk, dv`` like ``q`` and ``dbias`` like ``bias``, CPU tensors (pinned)
     group: with a process group, ``host`` holds this rank's rows and dBias is all-reduced once.
     Returns after everything has arrived in ``out``.
@@ -309,47 +312,78 @@ def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, 
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     q_h, b_h = host["q"], host["bias"]
     B, H, L1, L2, D = q_h.shape
+    assert L2 % 8 == 0 and D in (32, 64) and q_h.dtype in (torch.float16, torch.bfloat16)
     L = _cabi.lib()
     NSLOT = 3
     names_in, names_out = ("q", "k", "v", "do"), ("o", "dq", "dk", "dv")
     for t in [host[n] for n in names_in] + [out[n] for n in names_out]:
         assert t.is_contiguous() and t.shape == q_h.shape and t.dtype == q_h.dtype
+    dtype_code = _cabi.FTA_BF16 if q_h.dtype == torch.bfloat16 else _cabi.FTA_FP16
+    L2p = _l2p(L2)
     with torch.cuda.device(dev):
         cur = torch.cuda.current_stream(dev)
+        st = _status_of(dev)
+        st.raise_if_set()
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         sizes = _block_sizes(L1, block_rows)
         cap = max(sizes)
-        bufs = [{k: torch.empty((B, H, cap, L2, D), dtype=q_h.dtype, device=dev) for k in names_in}
-                for _ in range(NSLOT)]
+        mk = lambda *shape, dtype=q_h.dtype: torch.empty(shape, dtype=dtype, device=dev)
+        slots = [{**{k: mk(B, H, cap, L2, D) for k in names_in + names_out}, "ores": mk(B, H, cap, L2, D),
+                  "lse": mk(3, B, H, cap, L2p, dtype=torch.float32), "delta": mk(B, H, cap, L2p, dtype=torch.float32)}
+                 for _ in range(NSLOT)]
+        ws_bytes = int(L.fta_bwd_workspace_bytes(FtaProblem(B, H, cap, L2, D, dtype_code)))
+        ws = mk(ws_bytes, dtype=torch.uint8)
         ev_in = [torch.cuda.Event() for _ in range(NSLOT)]
         ev_comp = [torch.cuda.Event() for _ in range(NSLOT)]
+        ev_out = [torch.cuda.Event() for _ in range(NSLOT)]
         s_in.wait_stream(cur)
         with torch.cuda.stream(s_in):
             bias = b_h.to(dev, non_blocking=True)
+        cur.wait_stream(s_in)
+        bias_k = bias
+        if L2p != L2:
+            bias_k = mk(B, H, L2p, L2p)
+            check(L.fta_mask_bias(FtaProblem(B, H, 1, L2, D, dtype_code), t4(bias), None, bias_k.data_ptr(), cur.cuda_stream),
+                  "fta_mask_bias")
+        bias4 = t4(bias_k)
         db32 = torch.zeros((B, H, L2, L2), dtype=torch.float32, device=dev)
+        db_blk = torch.empty_like(db32)
+        resid = q_h.dtype == torch.bfloat16 and _SAVE_O_RESIDUAL
         r0 = 0
         for blk, n in enumerate(sizes):
             slot = blk % NSLOT
+            sl = slots[slot]
             if blk >= NSLOT:
-                s_in.wait_event(ev_comp[slot])  # the kernels of block blk - NSLOT have read this slot
+                s_in.wait_event(ev_comp[slot])  # the kernels of block blk - NSLOT have read this slot's inputs
+                cur.wait_event(ev_out[slot])    # ... and its results are on their way out of the output buffers
             for name in names_in:
-                _copy_rows(L, bufs[slot][name], 0, host[name], r0, n, s_in.cuda_stream)
+                _copy_rows(L, sl[name], 0, host[name], r0, n, s_in.cuda_stream)
             ev_in[slot].record(s_in)
             cur.wait_event(ev_in[slot])
-            qd, kd, vd = (bufs[slot][name][:, :, :n].detach().requires_grad_() for name in ("q", "k", "v"))
-            o = _attention.apply(qd, kd, vd, bias.detach().requires_grad_(), sm_scale, None, None)
-            o.backward(bufs[slot]["do"][:, :, :n])
-            db32 += _last["dbias_f32"]
+            prob = FtaProblem(B, H, n, L2, D, dtype_code)
+            v5 = {k: t5(sl[k][:, :, :n]) for k in names_in + names_out}
+            ores_ptr = sl["ores"].data_ptr() if resid else None
+            # the residual buffer is addressed with the strides of `o` (the slot's full block)
+            check(L.fta_forward(prob, v5["q"], v5["k"], v5["v"], bias4, float(sm_scale), v5["o"], ores_ptr,
+                                sl["lse"].data_ptr(), st.word.data_ptr(), cur.cuda_stream), "fta_forward")
+            check(L.fta_bwd_preprocess(prob, v5["o"], ores_ptr, v5["do"], sl["delta"].data_ptr(), cur.cuda_stream),
+                  "fta_bwd_preprocess")
+            check(L.fta_backward(prob, v5["q"], v5["k"], v5["v"], bias4, v5["do"], sl["lse"].data_ptr(),
+                                 sl["delta"].data_ptr(), float(sm_scale), v5["dq"], v5["dk"], v5["dv"],
+                                 db_blk.data_ptr(), None, ws.data_ptr(), ws_bytes, st.word.data_ptr(), cur.cuda_stream),
+                  "fta_backward")
+            db32 += db_blk
             ev_comp[slot].record(cur)
             s_out.wait_event(ev_comp[slot])
-            for name, t in (("o", o.detach()), ("dq", qd.grad), ("dk", kd.grad), ("dv", vd.grad)):
-                t.record_stream(s_out)  # results are dense (B, H, n, L2, D) tensors of this block
-                _copy_rows(L, out[name], r0, t, 0, n, s_out.cuda_stream)
+            for name in names_out:
+                _copy_rows(L, out[name], r0, sl[name], 0, n, s_out.cuda_stream)
+            ev_out[slot].record(s_out)
             r0 += n
         if group is not None:
             torch.distributed.all_reduce(db32, op=torch.distributed.ReduceOp.SUM, group=group)
         out["dbias"].copy_(db32.to(b_h.dtype), non_blocking=True)
         _last["dbias_f32"] = db32
+        st.publish()
         cur.wait_stream(s_out)
         torch.cuda.synchronize(dev)
     check_device_status(dev)
