@@ -47,7 +47,7 @@ METRIC = "fwd+bwd TFLOP/s, fused triangle attention B=1 H=4 L=768 D=32 bf16"
 # from the one-pass ncu capture of that launch (dram__bytes_read.sum + dram__bytes_write.sum,
 # profiles/bwd_kernel_ns_l768_dram.md); a rank that owns a fraction of the rows and heads moves that
 # fraction of it.
-BWD_KERNEL_DRAM_BYTES = 1228830208 + 1208799488
+BWD_KERNEL_DRAM_BYTES = 1152078848 + 1059723264
 # L1 rows per block of the end-to-end leg (host tensors streamed through the GPU)
 E2E_BLOCK_ROWS = int(os.environ.get("FTA_E2E_BLOCK_ROWS", "96"))
 
