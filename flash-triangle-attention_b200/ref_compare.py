@@ -48,7 +48,7 @@ def load_naive_fn(path: str = REF_MODULE):
     return ns["reference_tt_attn"]
 
 
-def triton_supports(L1: int, L2: int, D: int, dtype, backward: bool) -> str | None:
+def triton_supports(L1: int, L2: int, D: int, dtype, backward: bool, batch_heads: int = 1) -> str | None:
     """None when the reference's Triton path can run the case, else the reason it cannot."""
     import torch
     if dtype != torch.float16:
@@ -61,6 +61,9 @@ def triton_supports(L1: int, L2: int, D: int, dtype, backward: bool) -> str | No
         return "reference cannot run this case: L must be a multiple of 128 (no boundary checks)"
     if backward and (L2 & (L2 - 1)) != 0:
         return "reference cannot run this case: its backward needs L a power of two"
+    if backward and batch_heads * L1 > 65535:
+        # its backward launches put B*H*L1 on the y / z axis of the grid (flash_tt_attn.py:630, 644)
+        return "reference cannot run this case: B*H*L1 exceeds the 65535 limit of the grid axis its backward uses"
     return None
 
 
@@ -131,7 +134,7 @@ def compare_with_triton(ours_attention, steps: int = 10, warmup: int = 3, cases=
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     out = []
     for label, B, H, L, D, backward in cases:
-        why = triton_supports(L, L, D, torch.float16, backward)
+        why = triton_supports(L, L, D, torch.float16, backward, B * H)
         row = {"case": label, "B": B, "H": H, "L": L, "D": D, "dtype": "fp16", "mode": "fwd+bwd" if backward else "fwd"}
         if why:
             row["unavailable"] = why

@@ -7,12 +7,16 @@ peak memory (GB), and writes one CSV per (mode, metric) named
 ``L,<fused>,Vanilla PyTorch`` (flash_tt_attn.py:714-843, test_results/*.csv). This script writes
 the same files for this library so that B200 curves can be laid over the published ones:
 
-    python flash-triangle-attention_b200/sweep.py --out sweep_out [--dtype bf16] [--lmax 1024]
+    python flash-triangle-attention_b200/sweep.py --out sweep_out [--dtype bf16|fp16] [--dim 32|64] [--lmax 2048]
 
-Lengths below 128 run through the padded path (keys padded to one 128-key tile). The vanilla
-column is the naive PyTorch statement of the op on the same GPU, skipped (empty cell) when its
-(B,H,L,L,L) logits would not fit in ``--vanilla-gb`` of memory. "bwd" times the backward pass only
-(forward outside the timed region), as the reference does.
+Lengths that are not a multiple of 128 run natively (ragged blocks are padded by the tile loads).
+The vanilla column is the naive PyTorch statement of the op on the same GPU, skipped (empty cell)
+when its (B,H,L,L,L) logits would not fit in ``--vanilla-gb`` of memory. With ``--dtype fp16`` and
+a copy of the reference under baseline/_ref a third column, ``Triton [FP16]`` (the reference's own
+header), holds the reference's Triton kernels on the same GPU for the lengths they can run
+(forward: L a multiple of 128; backward: L a power of two >= 128; empty elsewhere - its published
+L < 128 rows read out of bounds or launch an empty grid, flash_tt_attn.py:618, 644). "bwd" times the
+backward pass only (forward outside the timed region), as the reference does.
 """
 from __future__ import annotations
 
@@ -27,6 +31,7 @@ sys.path.insert(0, HERE)
 import torch  # noqa: E402
 
 import flash_tt_attn as fta  # noqa: E402
+import ref_compare  # noqa: E402
 
 
 def _time_ms(fn, reps, flush):
@@ -53,7 +58,9 @@ def _measure(provider, mode, metric, B, H, L, D, dtype, reps, flush):
                for _ in range(3)]
     bias = torch.randn(B, H, L, L, device=dev, dtype=dtype, generator=g).requires_grad_(mode == "bwd")
     scale = D ** -0.5
-    op = fta.attention if provider == "fused" else fta.reference_tt_attn
+    op = {"fused": fta.attention, "vanilla": fta.reference_tt_attn}.get(provider)
+    if provider == "triton":
+        op = ref_compare.load_triton_module().attention
     torch.cuda.reset_peak_memory_stats()
     if mode == "fwd":
         fn = lambda: op(q, k, v, bias, scale)  # noqa: E731
@@ -76,7 +83,7 @@ def main():
     ap.add_argument("--heads", type=int, default=8)
     ap.add_argument("--dim", type=int, default=32)
     ap.add_argument("--lmin", type=int, default=16)
-    ap.add_argument("--lmax", type=int, default=1024)
+    ap.add_argument("--lmax", type=int, default=2048)
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--vanilla-gb", type=float, default=40.0)
     a = ap.parse_args()
@@ -90,19 +97,26 @@ def main():
         Ls.append(L)
         L *= 2
     fused_name = f"B200 fused [{a.dtype.upper()}]"
+    with_triton = dtype == torch.float16 and ref_compare.available()
     for mode in ("fwd", "bwd"):
         for metric in ("latency", "memory"):
             path = os.path.join(a.out, f"fused-attention-batch{B}-head{H}-d{D}-{mode}-{metric}.csv")
             with open(path, "w", newline="") as f:
                 wr = csv.writer(f)
-                wr.writerow(["L", fused_name, "Vanilla PyTorch"])
+                wr.writerow(["L", fused_name, "Vanilla PyTorch"] + (["Triton [FP16]"] if with_triton else []))
                 for L in Ls:
                     ours = _measure("fused", mode, metric, B, H, L, D, dtype, a.reps, flush)
                     logits_gb = B * H * L * L * L * 4 * (3 if mode == "bwd" else 2) / 2 ** 30
                     van = ""
                     if logits_gb <= a.vanilla_gb:
                         van = f"{_measure('vanilla', mode, metric, B, H, L, D, dtype, a.reps, flush):.6f}"
-                    wr.writerow([f"{float(L):.6f}", f"{ours:.6f}", van])
+                    row = [f"{float(L):.6f}", f"{ours:.6f}", van]
+                    if with_triton:
+                        tri = ""
+                        if ref_compare.triton_supports(L, L, D, dtype, mode == "bwd", B * H) is None:
+                            tri = f"{_measure('triton', mode, metric, B, H, L, D, dtype, a.reps, flush):.6f}"
+                        row.append(tri)
+                    wr.writerow(row)
                     f.flush()
             print("wrote", path)
     fta.check_device_status()
