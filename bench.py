@@ -391,21 +391,33 @@ def main():
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         sharded = grp is not None
 
-        def step(ef=None):
+        def step(ef=None, marks=None):
+            """One pass. `ef`: event recorded after the forward. `marks`: dict that receives an event after
+            every call (the per-launch diagnostic loop below; never used in the timed region)."""
+            def mark(name):
+                if marks is not None:
+                    marks[name] = torch.cuda.Event(enable_timing=True)
+                    marks[name].record()
+            mark("start")
             _cabi.check(L.fta_forward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), scale, t5(o),
                                       o_res.data_ptr(), lse.data_ptr(), status.data_ptr(), stream), "fta_forward")
             if ef is not None:
                 ef.record()
+            mark("forward")
             _cabi.check(L.fta_bwd_preprocess(prob, t5(o), o_res.data_ptr(), t5(d["do"]), delta.data_ptr(), stream),
                         "fta_bwd_preprocess")
+            mark("preprocess")
             _cabi.check(L.fta_backward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), t5(d["do"]),
                                        lse.data_ptr(), delta.data_ptr(), scale, t5(dq), t5(dk), t5(dv),
                                        db32.data_ptr(), None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
                                        status.data_ptr(), stream), "fta_backward")
+            mark("backward")
             if sharded:
                 dist.all_reduce(db32, group=grp)
+                mark("allreduce")
                 _cabi.check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
                             "fta_dbias_cast")
+                mark("cast")
 
         for _ in range(warmup):
             step()
@@ -435,7 +447,36 @@ def main():
         bwdk_ms = [k0.elapsed_time(k1) for e0, e1, ef, k0, k1 in evs]
         barrier()
         wall = time.perf_counter() - wall0
+        # ---- per-launch diagnostic loop (outside the timed region): an event after every call, and the
+        # two events fta_backward records around its main kernel split that call into bias transposition
+        # + zero fill / kernel / dQ + dBias finalise. Events between launches cost a little, so the sum
+        # can exceed ms_per_step.
+        diag_rows = []
+        for _ in range(min(10, steps)):
+            flush.zero_()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record()
+            k1.record()
+            L.fta_profile_backward_kernel(k0.cuda_event, k1.cuda_event)
+            marks = {}
+            step(None, marks)
+            diag_rows.append((marks, k0, k1))
+        torch.cuda.synchronize()
         L.fta_profile_backward_kernel(None, None)
+        def _ms(a, b):
+            return float(np.mean([m[a].elapsed_time(m[b]) for m, _k0, _k1 in diag_rows]))
+        launch_ms = {
+            "forward": _ms("start", "forward"),
+            "preprocess": _ms("forward", "preprocess"),
+            "bwd_prologue": float(np.mean([m["preprocess"].elapsed_time(k0) for m, k0, k1 in diag_rows])),
+            "bwd_kernel": float(np.mean([k0.elapsed_time(k1) for m, k0, k1 in diag_rows])),
+            "bwd_epilogue": float(np.mean([k1.elapsed_time(m["backward"]) for m, k0, k1 in diag_rows])),
+        }
+        if sharded:
+            launch_ms["dbias_allreduce"] = _ms("backward", "allreduce")
+            launch_ms["dbias_cast"] = _ms("allreduce", "cast")
+        launch_ms = {k: round(v, 4) for k, v in launch_ms.items()}
+        barrier()
         clocks = sampler.stop() if sampler else None
         if int(status.item()) != 0:
             raise SystemExit(f"device status 0x{int(status.item()):x}: a bounded device-side wait ran out")
@@ -448,6 +489,7 @@ def main():
                 "wall_ms_per_step_incl_flush": wall / steps * 1e3, "heads_per_gpu": H, "rows_per_gpu": nrows,
                 "allreduce_ranks": 1 if grp is None else dist.get_world_size(grp),
                 "launches_per_step": 5 + (1 if sharded else 0),  # fwd, preprocess, bwd prologue / kernel / epilogue (+ cast)
+                "launch_ms": launch_ms,
                 "host": host, "grp": grp}
 
     main_res = time_partition(args.shard, args.steps, True)
@@ -455,7 +497,7 @@ def main():
     if world > 1:
         other_mode = "rows" if args.shard == "heads" else "heads"
         other = time_partition(other_mode, max(5, args.steps // 2), False)
-        other = {k: other[k] for k in ("value", "ms_per_step", "fwd_ms", "bwd_kernel_ms", "allreduce_ranks",
+        other = {k: other[k] for k in ("value", "ms_per_step", "fwd_ms", "bwd_kernel_ms", "launch_ms", "allreduce_ranks",
                                        "heads_per_gpu", "rows_per_gpu")}
         other["shard"] = other_mode
 
@@ -546,7 +588,8 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
             "detail": {"heads_per_gpu": r["heads_per_gpu"], "rows_per_gpu": r["rows_per_gpu"],
                        "dbias_allreduce_ranks": r["allreduce_ranks"], "fwd_ms": r["fwd_ms"],
-                       "bwd_kernel_ms": r["bwd_kernel_ms"], "frac_of_bf16_peak": r["value"] / (peak_tf * world),
+                       "bwd_kernel_ms": r["bwd_kernel_ms"], "launch_ms": r["launch_ms"],
+                       "frac_of_bf16_peak": r["value"] / (peak_tf * world),
                        "peak": f"{peak_tf} TFLOP/s {peak_kind}",
                        "wall_ms_per_step_incl_flush": r["wall_ms_per_step_incl_flush"]},
             "e2e": e2e if e2e is not None else {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,

@@ -282,12 +282,36 @@ __global__ void __launch_bounds__(256) bwd_epilogue_kernel(const float* __restri
 #pragma unroll
   for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool q_in = q0 + qc < L2;
-  for (int pl = 0; pl < nplanes; ++pl) {  // fixed order
+  // planes added in index order (bit-reproducible); the loads of four planes are in flight together:
+  // with one head per GPU there are only (L2/64)^2 of these blocks and up to 24 planes each, a chain
+  // of dependent memory latencies when the planes are read one at a time
+  auto load = [&](int pl, int i) {
+    return __ldg(reinterpret_cast<const float4*>(src + static_cast<long long>(pl) * plane_stride +
+                                                 static_cast<long long>(16 * i) * L2));
+  };
+  int pl = 0;
+  for (; pl + 4 <= nplanes; pl += 4) {
+    float4 x[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        x[u][i] = (q_in && k0 + kr + 16 * i < L2) ? load(pl + u, i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i].x += x[u][i].x;
+        acc[i].y += x[u][i].y;
+        acc[i].z += x[u][i].z;
+        acc[i].w += x[u][i].w;
+      }
+  }
+  for (; pl < nplanes; ++pl) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       if (!q_in || k0 + kr + 16 * i >= L2) continue;
-      const float4 x = __ldg(reinterpret_cast<const float4*>(src + static_cast<long long>(pl) * plane_stride +
-                                                             static_cast<long long>(16 * i) * L2));
+      const float4 x = load(pl, i);
       acc[i].x += x.x;
       acc[i].y += x.y;
       acc[i].z += x.z;
