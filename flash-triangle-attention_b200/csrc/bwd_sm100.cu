@@ -873,10 +873,23 @@ int bwd_num_planes(int B, int H, int L1, int L2, int D, int num_sms) {
     // time ~ waves * chain ; work ~ base * L1 / num_sms
     return (static_cast<double>(base) * L1 / num_sms) / (static_cast<double>(waves) * chain);
   };
-  double best_eff = -1.0;
-  for (int np = 1; np <= np_max; ++np) best_eff = efficiency(np) > best_eff ? efficiency(np) : best_eff;
-  // The planes are updated in place all through the kernel, so their footprint should stay
-  // inside the L2 cache: take the FEWEST planes whose schedule is within 7 % of the best one.
+  // The planes are updated in place all through the kernel, so their footprint should stay inside
+  // the L2 cache. While it does (half of the 126 MB), take the best schedule, and the fewest planes
+  // among schedules within 1 % of it; beyond that, the FEWEST planes whose schedule is within 7 % of
+  // the best one.
+  const long long l2p = (L2 + 127) / 128 * 128;
+  const double plane_set_bytes = 4.0 * B * H * static_cast<double>(l2p) * l2p;
+  const double budget = 64.0 * 1024 * 1024;
+  double best_small = -1.0, best_eff = -1.0;
+  for (int np = 1; np <= np_max; ++np) {
+    const double e = efficiency(np);
+    best_eff = e > best_eff ? e : best_eff;
+    if (np * plane_set_bytes <= budget) best_small = e > best_small ? e : best_small;
+  }
+  if (best_small >= 0.93 * best_eff) {
+    for (int np = 1; np <= np_max; ++np)
+      if (np * plane_set_bytes <= budget && efficiency(np) >= 0.99 * best_small) return np;
+  }
   for (int np = 1; np <= np_max; ++np)
     if (efficiency(np) >= 0.93 * best_eff) return np;
   return 1;
