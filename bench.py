@@ -565,6 +565,8 @@ def main():
         t_in, t_out, t_both = copy_ms(True, False), copy_ms(False, True), copy_ms(True, True)
         e2e = {"value": flops_step / (e2e_ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "steps": e2e_steps, "ms_per_step": e2e_ms_step,
+               # this rank's median beside the mean: the host link is shared, single steps of 25-28 ms occur
+               "ms_per_step_median": float(np.median(e2e_ms)),
                "h2d_only_gbs": h2d / t_in / 1e6, "d2h_only_gbs": d2h / t_out / 1e6,
                "copy_bound_ms": t_both, "frac_of_copy_bound": t_both / e2e_ms_step,
                "note": "per rank: its shard of q,k,v,dO + bias in, o,dq,dk,dv + dbias out; copy_bound_ms = the same "
