@@ -107,6 +107,22 @@ def test_backward_rejects_small_workspace_and_null():
     assert lib.fta_bwd_workspace_bytes(FtaProblem(1, 1, 4, 100, 32, 1)) == 0
 
 
+def test_plane_count_follows_the_schedule():
+    """The number of private dBias planes = row blocks per (head, key block). Without a GPU the
+    library assumes 148 SMs. While the planes fit half the L2 the best single-wave schedule wins
+    (one head: 24 planes of 32 rows, not 23 of 34); when they do not, the fewest planes within 7 %."""
+    lib = _cabi.lib()
+    planes = lambda B, H, L1, L2, D: lib.fta_bwd_num_planes(FtaProblem(B, H, L1, L2, D, 1))
+    assert planes(1, 4, 768, 768, 32) == 6      # the headline shape: 144 CTAs of 128 rows
+    assert planes(1, 1, 768, 768, 32) == 24     # one head per GPU (4 GPUs): 144 CTAs of 32 rows
+    assert planes(1, 1, 384, 768, 32) == 24     # one head x half the rows (8 GPUs)
+    assert planes(1, 2, 768, 768, 32) == 12
+    assert planes(1, 8, 2048, 2048, 64) == 8    # 134 MB per plane set: the tolerant rule
+    for shape in ((1, 4, 1, 128, 32), (2, 3, 7, 136, 64), (4, 8, 256, 256, 32)):
+        n = planes(*shape)
+        assert 1 <= n <= 64 and n <= shape[2]
+
+
 def test_dbias_cast_argument_checks():
     lib = _cabi.lib()
     assert lib.fta_dbias_cast(None, 0x1000, 16, 1, None) == -1
