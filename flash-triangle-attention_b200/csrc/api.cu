@@ -293,6 +293,19 @@ int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* 
   return FTA_OK;
 }
 
+int fta_dbias_sum_peers(const float* const* parts, int32_t nranks, int64_t n, float* out_f32, void* out_cast,
+                        int32_t dtype, void* stream) {
+  if (!parts || (!out_f32 && !out_cast)) return FTA_ERR_NULL;
+  if (nranks < 1 || nranks > 64 || n <= 0 || n % 8 != 0) return FTA_ERR_SHAPE;
+  if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(parts) & 7u) || (out_f32 && !aligned16(out_f32)) || (out_cast && !aligned16(out_cast)))
+    return FTA_ERR_ALIGN;
+  if (const int e = fta::launch_dbias_sum_peers(parts, nranks, n, out_f32, out_cast, dtype == FTA_BF16,
+                                                static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
+  return FTA_OK;
+}
+
 int fta_memcpy_2d(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes, size_t width_bytes,
                   size_t rows, void* stream) {
   if (!dst || !src) return FTA_ERR_NULL;

@@ -92,6 +92,10 @@ int launch_bwd_epilogue(const float* dq32, void* dq, const long long sdq[4], int
                         float scale, const float* planes, int nplanes, float* dbias_f32, void* dbias_cast, bool bf16,
                         cudaStream_t stream);
 
+// out = sum over r of parts[r][0..n) (rank order), float32 and / or rounded to 16 bits; `parts`: device
+// array of `nranks` device pointers (peer mappings included); n a multiple of 8
+int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, float* out_f32, void* out_cast,
+                           bool bf16, cudaStream_t stream);
 // dst[i] = (dtype) src[i], n a multiple of 4
 int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaStream_t stream);
 

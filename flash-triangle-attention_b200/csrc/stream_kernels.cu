@@ -136,6 +136,40 @@ __global__ void __launch_bounds__(256) dbias_cast_kernel(const float* __restrict
   }
 }
 
+// dBias across GPUs without a library collective: every rank holds its float32 partial in memory
+// that its peers can address (NVLink peer mappings), and each rank adds the R partials itself, in
+// rank order (the same order on every rank: identical bits everywhere), then rounds once. `parts`
+// is a device array of R pointers, entry r = rank r's partial as seen from this GPU. Plain loads
+// that skip L1 (the peers rewrite these buffers between launches); 8 elements per thread, grid-stride.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) dbias_sum_peers_kernel(const float* const* __restrict__ parts, int nranks,
+                                                              long long n, float* __restrict__ out_f32,
+                                                              uint16_t* __restrict__ out_cast) {
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long nvec = n / 8;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += nthreads) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), c = a;
+    for (int r = 0; r < nranks; ++r) {
+      const float4* src = reinterpret_cast<const float4*>(parts[r]) + 2 * v;
+      const float4 x = __ldcg(src), y = __ldcg(src + 1);
+      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+      c.x += y.x; c.y += y.y; c.z += y.z; c.w += y.w;
+    }
+    if (out_f32) {
+      reinterpret_cast<float4*>(out_f32)[2 * v] = a;
+      reinterpret_cast<float4*>(out_f32)[2 * v + 1] = c;
+    }
+    if (out_cast) {
+      uint4 pk;
+      pk.x = pack2<kBf16>(a.x, a.y);
+      pk.y = pack2<kBf16>(a.z, a.w);
+      pk.z = pack2<kBf16>(c.x, c.y);
+      pk.w = pack2<kBf16>(c.z, c.w);
+      reinterpret_cast<uint4*>(out_cast)[v] = pk;
+    }
+  }
+}
+
 // Padded, masked copy of the pair bias for problems whose L2 is not a multiple of 128 and / or that
 // drop keys with a boolean mask: out (B*H, L2p, L2p), 8 elements (16 bytes) per thread.
 template <bool kBf16>
@@ -466,6 +500,14 @@ int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaS
   const int grid = grid_for(n / 8 + 1, 256);
   if (bf16) dbias_cast_kernel<true><<<grid, 256, 0, stream>>>(src, n, static_cast<uint16_t*>(dst));
   else dbias_cast_kernel<false><<<grid, 256, 0, stream>>>(src, n, static_cast<uint16_t*>(dst));
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, float* out_f32, void* out_cast,
+                           bool bf16, cudaStream_t stream) {
+  const int grid = grid_for(n / 8, 256);
+  if (bf16) dbias_sum_peers_kernel<true><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, static_cast<uint16_t*>(out_cast));
+  else dbias_sum_peers_kernel<false><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, static_cast<uint16_t*>(out_cast));
   return static_cast<int>(cudaGetLastError());
 }
 

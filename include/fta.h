@@ -160,6 +160,20 @@ FTA_API int fta_backward(const FtaProblem* prob, const FtaTensor5* q, const FtaT
  * flash_tt_attn.py:425-426, 613). */
 FTA_API int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype, void* stream);
 
+/* The cross-GPU sum of dBias and its rounding in one kernel, over peer memory instead of a
+ * library collective: out[i] = sum over r = 0 .. nranks-1 (in that order, so every rank gets the same
+ * bits) of parts[r][i], written as float32 (`out_f32`, may be NULL) and / or rounded to the bias
+ * dtype (`out_cast`, may be NULL). `parts` is a DEVICE array of `nranks` device pointers: entry r
+ * addresses rank r's float32 partial (the `dbias_f32` of its fta_backward) as this GPU sees it - its
+ * own buffer, or a peer mapping (CUDA IPC / virtual-memory export, NVLink). n a multiple of 8, buffers
+ * 16-byte aligned. The kernel only reads and adds: the caller makes sure that every rank's partial is
+ * complete before this launch (a barrier between the ranks on the streams involved) and is not
+ * rewritten until every rank's launch has finished (e.g. two partial buffers used in turn). Stands
+ * where the reference has its fp16 atomics into one buffer (flash_tt_attn.py:425-426): the
+ * reference itself is single-GPU. */
+FTA_API int fta_dbias_sum_peers(const float* const* parts, int32_t nranks, int64_t n, float* out_f32,
+                        void* out_cast, int32_t dtype, void* stream);
+
 /* Backward pass without a caller-provided workspace. It has no counterpart in the reference.
  * For callers that cannot allocate device memory where they call this library (a framework's
  * memory-planning phase, a plugin interface that only passes inputs and outputs, a loop that

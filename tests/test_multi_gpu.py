@@ -52,3 +52,55 @@ def test_two_gpu_row_sharding_matches_oracle(tmp_path):
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + os.getpid() % 400), str(script)]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+
+
+_PEER_WORKER = r"""
+import os, sys
+sys.path.insert(0, {root!r}); sys.path.insert(0, os.path.join({root!r}, "flash-triangle-attention_b200"))
+import torch, torch.distributed as dist
+import flash_tt_attn as fta
+import _cabi
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+dev = torch.device("cuda", rank)
+B, H, L2 = 1, 2, 256
+peer = fta.PeerDbiasSum((B, H, L2, L2), dist.group.WORLD, dev, torch.bfloat16)
+L = _cabi.lib()
+stream = torch.cuda.current_stream().cuda_stream
+for step in range(5):   # both partial buffers, several times over
+    g = torch.Generator(device=dev).manual_seed(100 * step + rank)
+    part = torch.randn(B, H, L2, L2, device=dev, generator=g) * 3.0
+    peer.partial().copy_(part)
+    out16 = torch.empty(B, H, L2, L2, dtype=torch.bfloat16, device=dev)
+    out32 = torch.empty(B, H, L2, L2, dtype=torch.float32, device=dev)
+    peer.reduce(out16, out32)
+    ref = part.clone()
+    dist.all_reduce(ref)          # NCCL, same two addends: a + b either way
+    torch.cuda.synchronize()
+    assert torch.equal(out32, ref), (step, float((out32 - ref).abs().max()))
+    assert torch.equal(out16, ref.to(torch.bfloat16))
+    # every rank holds the same bits
+    both = [torch.empty_like(out32) for _ in range(world)]
+    dist.all_gather(both, out32)
+    assert torch.equal(both[0], both[1])
+# argument checks of the entry point, no launch
+assert L.fta_dbias_sum_peers(None, 2, 64, None, out16.data_ptr(), 1, stream) == -1
+assert L.fta_dbias_sum_peers(peer.parts[0].data_ptr(), 2, 60, None, out16.data_ptr(), 1, stream) == -2
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_gpu_dbias_sum_over_peer_memory_equals_the_allreduce(tmp_path):
+    """fta_dbias_sum_peers through PeerDbiasSum (symmetric memory, plain peer loads, no multicast)
+    gives the bits of the NCCL all-reduce + cast on both ranks, step after step."""
+    script = tmp_path / "peer_worker.py"
+    script.write_text(_PEER_WORKER.format(root=ROOT))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(29900 + os.getpid() % 90), str(script)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
