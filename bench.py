@@ -299,6 +299,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "triton"])
     ap.add_argument("--shard", default="heads", choices=["heads", "rows"],
                     help="multi-GPU partition of the headline value (the other one is reported beside it)")
+    ap.add_argument("--dbias-sum", default="auto", choices=["auto", "nccl", "peer"],
+                    help="ranks that share a head sum dBias with an NCCL all-reduce + cast, or with "
+                         "fta_dbias_sum_peers over NVLink peer memory (auto: peer for groups of two)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-triton", action="store_true", help="skip the reference-Triton comparison table")
@@ -390,6 +393,16 @@ def main():
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         sharded = grp is not None
+        # how the ranks of a group sum dBias: every rank reading its peers' partials pays for a pair,
+        # the NCCL all-reduce for larger groups
+        peer = None
+        if sharded and (args.dbias_sum == "peer" or (args.dbias_sum == "auto" and dist.get_world_size(grp) == 2)):
+            try:
+                peer = fta.PeerDbiasSum(db32.shape, grp, dev, dt)
+            except Exception as e:  # symmetric memory unavailable: the all-reduce does it
+                if args.dbias_sum == "peer":
+                    raise
+                print(f"[bench] peer-memory dBias sum unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
 
         def step(ef=None, marks=None):
             """One pass. `ef`: event recorded after the forward. `marks`: dict that receives an event after
@@ -409,10 +422,14 @@ def main():
             mark("preprocess")
             _cabi.check(L.fta_backward(prob, t5(d["q"]), t5(d["k"]), t5(d["v"]), t4(d["bias"]), t5(d["do"]),
                                        lse.data_ptr(), delta.data_ptr(), scale, t5(dq), t5(dk), t5(dv),
-                                       db32.data_ptr(), None if sharded else db.data_ptr(), ws.data_ptr(), ws_bytes,
-                                       status.data_ptr(), stream), "fta_backward")
+                                       (peer.partial() if peer else db32).data_ptr(), None if sharded else db.data_ptr(),
+                                       ws.data_ptr(), ws_bytes, status.data_ptr(), stream), "fta_backward")
             mark("backward")
-            if sharded:
+            if peer:
+                peer.reduce(db, None, stream)  # barrier between the ranks + one kernel: sum in rank order, round
+                mark("allreduce")
+                mark("cast")
+            elif sharded:
                 dist.all_reduce(db32, group=grp)
                 mark("allreduce")
                 _cabi.check(L.fta_dbias_cast(db32.data_ptr(), db.data_ptr(), db32.numel(), prob.dtype, stream),
@@ -488,7 +505,8 @@ def main():
                 "fwd_ms": float(np.mean(fwd_ms)), "bwd_kernel_ms": float(np.mean(bwdk_ms)), "clocks": clocks,
                 "wall_ms_per_step_incl_flush": wall / steps * 1e3, "heads_per_gpu": H, "rows_per_gpu": nrows,
                 "allreduce_ranks": 1 if grp is None else dist.get_world_size(grp),
-                "launches_per_step": 5 + (1 if sharded else 0),  # fwd, preprocess, bwd prologue / kernel / epilogue (+ cast)
+                "launches_per_step": 5 + (1 if sharded else 0),  # fwd, preprocess, bwd prologue / kernel / epilogue (+ cast or peer sum)
+                "dbias_sum": "none" if not sharded else ("peer memory (fta_dbias_sum_peers)" if peer else "nccl all-reduce + cast"),
                 "launch_ms": launch_ms,
                 "host": host, "grp": grp}
 
@@ -497,7 +515,7 @@ def main():
     if world > 1:
         other_mode = "rows" if args.shard == "heads" else "heads"
         other = time_partition(other_mode, max(5, args.steps // 2), False)
-        other = {k: other[k] for k in ("value", "ms_per_step", "fwd_ms", "bwd_kernel_ms", "launch_ms", "allreduce_ranks",
+        other = {k: other[k] for k in ("value", "ms_per_step", "fwd_ms", "bwd_kernel_ms", "launch_ms", "allreduce_ranks", "dbias_sum",
                                        "heads_per_gpu", "rows_per_gpu")}
         other["shard"] = other_mode
 
@@ -589,7 +607,7 @@ def main():
             "warmup": warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg,
             "detail": {"heads_per_gpu": r["heads_per_gpu"], "rows_per_gpu": r["rows_per_gpu"],
-                       "dbias_allreduce_ranks": r["allreduce_ranks"], "fwd_ms": r["fwd_ms"],
+                       "dbias_allreduce_ranks": r["allreduce_ranks"], "dbias_sum": r["dbias_sum"], "fwd_ms": r["fwd_ms"],
                        "bwd_kernel_ms": r["bwd_kernel_ms"], "launch_ms": r["launch_ms"],
                        "frac_of_bf16_peak": r["value"] / (peak_tf * world),
                        "peak": f"{peak_tf} TFLOP/s {peak_kind}",

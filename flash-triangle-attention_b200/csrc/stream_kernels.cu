@@ -145,27 +145,54 @@ template <bool kBf16>
 __global__ void __launch_bounds__(256) dbias_sum_peers_kernel(const float* const* __restrict__ parts, int nranks,
                                                               long long n, float* __restrict__ out_f32,
                                                               uint16_t* __restrict__ out_cast) {
+  // Four 8-element vectors per thread and pass, each rank's eight 16-byte loads issued together: a
+  // peer load takes a few microseconds over NVLink, so the bytes in flight decide the rate.
+  constexpr int U = 4;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long nvec = n / 8;
-  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += nthreads) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), c = a;
-    for (int r = 0; r < nranks; ++r) {
-      const float4* src = reinterpret_cast<const float4*>(parts[r]) + 2 * v;
-      const float4 x = __ldcg(src), y = __ldcg(src + 1);
-      a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-      c.x += y.x; c.y += y.y; c.z += y.z; c.w += y.w;
+  for (long long v0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += U * nthreads) {
+    float4 acc[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u][0] = acc[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < nranks; ++r) {  // rank order: the same bits on every rank
+      const float4* src = reinterpret_cast<const float4*>(parts[r]);
+      float4 x[U][2];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * nthreads;
+        if (v < nvec) {
+          x[u][0] = __ldcg(src + 2 * v);
+          x[u][1] = __ldcg(src + 2 * v + 1);
+        } else {
+          x[u][0] = x[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          acc[u][hlf].x += x[u][hlf].x;
+          acc[u][hlf].y += x[u][hlf].y;
+          acc[u][hlf].z += x[u][hlf].z;
+          acc[u][hlf].w += x[u][hlf].w;
+        }
     }
-    if (out_f32) {
-      reinterpret_cast<float4*>(out_f32)[2 * v] = a;
-      reinterpret_cast<float4*>(out_f32)[2 * v + 1] = c;
-    }
-    if (out_cast) {
-      uint4 pk;
-      pk.x = pack2<kBf16>(a.x, a.y);
-      pk.y = pack2<kBf16>(a.z, a.w);
-      pk.z = pack2<kBf16>(c.x, c.y);
-      pk.w = pack2<kBf16>(c.z, c.w);
-      reinterpret_cast<uint4*>(out_cast)[v] = pk;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * nthreads;
+      if (v >= nvec) continue;
+      if (out_f32) {
+        reinterpret_cast<float4*>(out_f32)[2 * v] = acc[u][0];
+        reinterpret_cast<float4*>(out_f32)[2 * v + 1] = acc[u][1];
+      }
+      if (out_cast) {
+        uint4 pk;
+        pk.x = pack2<kBf16>(acc[u][0].x, acc[u][0].y);
+        pk.y = pack2<kBf16>(acc[u][0].z, acc[u][0].w);
+        pk.z = pack2<kBf16>(acc[u][1].x, acc[u][1].y);
+        pk.w = pack2<kBf16>(acc[u][1].z, acc[u][1].w);
+        reinterpret_cast<uint4*>(out_cast)[v] = pk;
+      }
     }
   }
 }
@@ -505,7 +532,7 @@ int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaS
 
 int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, float* out_f32, void* out_cast,
                            bool bf16, cudaStream_t stream) {
-  const int grid = grid_for(n / 8, 256);
+  const int grid = grid_for((n / 8 + 3) / 4, 256);
   if (bf16) dbias_sum_peers_kernel<true><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, static_cast<uint16_t*>(out_cast));
   else dbias_sum_peers_kernel<false><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, static_cast<uint16_t*>(out_cast));
   return static_cast<int>(cudaGetLastError());
