@@ -296,20 +296,27 @@ class PeerDbiasSum:
         base = [int(p) for p in self.hdl.buffer_ptrs]
         self.parts = [torch.tensor([p + slot * self.n * 4 for p in base], dtype=torch.int64, device=device)
                       for slot in (0, 1)]
+        self._views = [self.buf[slot].view(self.shape) for slot in (0, 1)]
+        self._ptrs = [v.data_ptr() for v in self._views]
+        self._parts_ptrs = [t.data_ptr() for t in self.parts]
+        self._lib = _cabi.lib()
         self.step = 0
 
     def partial(self):
         """This rank's float32 partial for the current step (pass it as ``dbias_f32``)."""
-        return self.buf[self.step & 1].view(self.shape)
+        return self._views[self.step & 1]
+
+    def partial_ptr(self):
+        return self._ptrs[self.step & 1]
 
     def reduce(self, out_cast, out_f32=None, stream=None):
         """After this rank's ``fta_backward`` has been enqueued: barrier, sum over the ranks, round."""
         stream = torch.cuda.current_stream(self.buf.device).cuda_stream if stream is None else stream
         self.hdl.barrier(channel=0)
-        check(_cabi.lib().fta_dbias_sum_peers(self.parts[self.step & 1].data_ptr(), self.world, self.n,
-                                              None if out_f32 is None else out_f32.data_ptr(),
-                                              None if out_cast is None else out_cast.data_ptr(), self.dtype_code,
-                                              stream), "fta_dbias_sum_peers")
+        check(self._lib.fta_dbias_sum_peers(self._parts_ptrs[self.step & 1], self.world, self.n,
+                                            None if out_f32 is None else out_f32.data_ptr(),
+                                            None if out_cast is None else out_cast.data_ptr(), self.dtype_code,
+                                            stream), "fta_dbias_sum_peers")
         self.step += 1
 
 
