@@ -301,7 +301,7 @@ def main():
                     help="multi-GPU partition of the headline value (the other one is reported beside it)")
     ap.add_argument("--dbias-sum", default="auto", choices=["auto", "nccl", "peer"],
                     help="ranks that share a head sum dBias with an NCCL all-reduce + cast, or with "
-                         "fta_dbias_sum_peers over NVLink peer memory (auto: peer for groups of two)")
+                         "fta_dbias_sum_peers[_sliced] over NVLink peer memory (auto: peer memory where available)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-triton", action="store_true", help="skip the reference-Triton comparison table")
@@ -393,10 +393,11 @@ def main():
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         sharded = grp is not None
-        # how the ranks of a group sum dBias: every rank reading its peers' partials pays for a pair,
-        # the NCCL all-reduce for larger groups
+        # how the ranks of a group sum dBias: over NVLink peer memory (a pair: each rank reads the other's
+        # partial; larger groups: each rank sums a slice and stores the result into every rank's buffer),
+        # or with an NCCL all-reduce + cast (--dbias-sum nccl, and wherever symmetric memory is unavailable)
         peer = None
-        if sharded and (args.dbias_sum == "peer" or (args.dbias_sum == "auto" and dist.get_world_size(grp) == 2)):
+        if sharded and args.dbias_sum in ("peer", "auto"):
             try:
                 peer = fta.PeerDbiasSum(db32.shape, grp, dev, dt)
             except Exception as e:  # symmetric memory unavailable: the all-reduce does it
@@ -431,7 +432,12 @@ def main():
                                        None if sharded else p_db, p_ws, ws_bytes, p_status, stream), "fta_backward")
             mark("backward")
             if peer:
-                peer.reduce(db, None, stream)  # barrier between the ranks + one kernel: sum in rank order, round
+                # barrier between the ranks + one kernel: sum in rank order, round (+ a second barrier
+                # where the result is stored into the peers' buffers)
+                if peer.sliced:
+                    peer.reduce_sliced(stream)
+                else:
+                    peer.reduce(db, None, stream)
                 mark("allreduce")
                 mark("cast")
             elif sharded:
@@ -510,7 +516,7 @@ def main():
                 "wall_ms_per_step_incl_flush": wall / steps * 1e3, "heads_per_gpu": H, "rows_per_gpu": nrows,
                 "allreduce_ranks": 1 if grp is None else dist.get_world_size(grp),
                 "launches_per_step": 5 + (1 if sharded else 0),  # fwd, preprocess, bwd prologue / kernel / epilogue (+ cast or peer sum)
-                "dbias_sum": "none" if not sharded else ("peer memory (fta_dbias_sum_peers)" if peer else "nccl all-reduce + cast"),
+                "dbias_sum": "none" if not sharded else (("peer memory (fta_dbias_sum_peers_sliced)" if peer.sliced else "peer memory (fta_dbias_sum_peers_sync: one launch)") if peer else "nccl all-reduce + cast"),
                 "launch_ms": launch_ms,
                 "host": host, "grp": grp}
 

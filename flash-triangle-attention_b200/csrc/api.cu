@@ -300,8 +300,36 @@ int fta_dbias_sum_peers(const float* const* parts, int32_t nranks, int64_t n, fl
   if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
   if ((reinterpret_cast<uintptr_t>(parts) & 7u) || (out_f32 && !aligned16(out_f32)) || (out_cast && !aligned16(out_cast)))
     return FTA_ERR_ALIGN;
-  if (const int e = fta::launch_dbias_sum_peers(parts, nranks, n, out_f32, out_cast, dtype == FTA_BF16,
-                                                static_cast<cudaStream_t>(stream)))
+  if (const int e = fta::launch_dbias_sum_peers(parts, nranks, n, out_f32, out_cast, dtype == FTA_BF16, nullptr, 0, 0, 0,
+                                                nullptr, static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
+  return FTA_OK;
+}
+
+int fta_dbias_sum_peers_sync(const float* const* parts, int32_t* const* flags, int32_t nranks, int32_t rank,
+                             int32_t epoch, int64_t n, float* out_f32, void* out_cast, int32_t dtype,
+                             uint64_t wait_limit_ns, int32_t* status, void* stream) {
+  if (!parts || !flags || !status || (!out_f32 && !out_cast)) return FTA_ERR_NULL;
+  if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks || epoch <= 0 || n <= 0 || n % 8 != 0) return FTA_ERR_SHAPE;
+  if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(parts) & 7u) || (reinterpret_cast<uintptr_t>(flags) & 7u) ||
+      (out_f32 && !aligned16(out_f32)) || (out_cast && !aligned16(out_cast)))
+    return FTA_ERR_ALIGN;
+  if (wait_limit_ns == 0) wait_limit_ns = 1000000000ull;
+  if (const int e = fta::launch_dbias_sum_peers(parts, nranks, n, out_f32, out_cast, dtype == FTA_BF16, flags, rank, epoch,
+                                                wait_limit_ns, status, static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
+  return FTA_OK;
+}
+
+int fta_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int32_t nranks, int32_t rank, int64_t n,
+                               int32_t dtype, void* stream) {
+  if (!parts || !outs) return FTA_ERR_NULL;
+  if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks || n <= 0 || n % 8 != 0) return FTA_ERR_SHAPE;
+  if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(parts) & 7u) || (reinterpret_cast<uintptr_t>(outs) & 7u)) return FTA_ERR_ALIGN;
+  if (const int e = fta::launch_dbias_sum_peers_sliced(parts, outs, nranks, rank, n, dtype == FTA_BF16,
+                                                       static_cast<cudaStream_t>(stream)))
     return cuda_fail(e);
   return FTA_OK;
 }

@@ -94,8 +94,14 @@ int launch_bwd_epilogue(const float* dq32, void* dq, const long long sdq[4], int
 
 // out = sum over r of parts[r][0..n) (rank order), float32 and / or rounded to 16 bits; `parts`: device
 // array of `nranks` device pointers (peer mappings included); n a multiple of 8
+// `flags` == nullptr: the caller has lined the ranks up; otherwise the kernel does (bounded wait, see the kernel)
 int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, float* out_f32, void* out_cast,
-                           bool bf16, cudaStream_t stream);
+                           bool bf16, int* const* flags, int rank, int epoch, unsigned long long limit_ns, int* status,
+                           cudaStream_t stream);
+// the same with the work split over the ranks: this rank sums its 1/nranks slice and stores the rounded
+// result into every rank's buffer `outs[r]` (device array of nranks device pointers)
+int launch_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int nranks, int rank, long long n,
+                                  bool bf16, cudaStream_t stream);
 // dst[i] = (dtype) src[i], n a multiple of 4
 int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaStream_t stream);
 

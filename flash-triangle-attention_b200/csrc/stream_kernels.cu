@@ -141,10 +141,50 @@ __global__ void __launch_bounds__(256) dbias_cast_kernel(const float* __restrict
 // rank order (the same order on every rank: identical bits everywhere), then rounds once. `parts`
 // is a device array of R pointers, entry r = rank r's partial as seen from this GPU. Plain loads
 // that skip L1 (the peers rewrite these buffers between launches); 8 elements per thread, grid-stride.
+// With `flags` (device array of R pointers: entry r = rank r's array of R 32-bit epoch words, as this GPU
+// sees it) the kernel also lines the ranks up itself, no barrier launch needed: block 0 publishes
+// "my partial of epoch e is complete" into every rank's word for this rank (the partial was written by
+// the previous kernel on the stream; fence + system-scope release), and every block waits until the R
+// words of this rank show epoch e before it reads the partials. The wait is bounded (`limit_ns` of the
+// global timer): when it runs out the kernel writes 0x1000 | 0x61 to `status` and returns without output.
+__device__ __forceinline__ void st_release_sys_u32(int* p, int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys_u32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(256) dbias_sum_peers_kernel(const float* const* __restrict__ parts, int nranks,
                                                               long long n, float* __restrict__ out_f32,
-                                                              uint16_t* __restrict__ out_cast) {
+                                                              uint16_t* __restrict__ out_cast, int* const* flags,
+                                                              int rank, int epoch, unsigned long long limit_ns,
+                                                              int* status) {
+  if (flags != nullptr) {
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < nranks) {
+      __threadfence_system();
+      st_release_sys_u32(flags[threadIdx.x] + rank, epoch);
+    }
+    bool ok = true;
+    if (static_cast<int>(threadIdx.x) < nranks) {
+      const int* mine = flags[rank] + threadIdx.x;
+      const unsigned long long t0 = global_timer_ns();
+      // epochs only grow; "at least" tolerates a peer that is already a step ahead
+      while (ld_acquire_sys_u32(mine) - epoch < 0) {
+        if (global_timer_ns() - t0 > limit_ns) {
+          ok = false;
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+    if (!__syncthreads_and(ok)) {
+      if (threadIdx.x == 0) atomicCAS(status, kStatusOk, kStatusWaitTimeout | 0x61);
+      return;
+    }
+  }
   // Four 8-element vectors per thread and pass, each rank's eight 16-byte loads issued together: a
   // peer load takes a few microseconds over NVLink, so the bytes in flight decide the rate.
   constexpr int U = 4;
@@ -193,6 +233,62 @@ __global__ void __launch_bounds__(256) dbias_sum_peers_kernel(const float* const
         pk.w = pack2<kBf16>(acc[u][1].z, acc[u][1].w);
         reinterpret_cast<uint4*>(out_cast)[v] = pk;
       }
+    }
+  }
+}
+
+// The same sum for larger groups, as reduce-scatter + all-gather in one kernel: rank `rank` adds the R
+// partials of ITS 1/R slice of the elements (rank order), rounds, and stores the 16-bit result into
+// every rank's output buffer (`outs`: device array of R pointers, peer mappings included). Each rank
+// then reads (R-1)/R of one partial and writes (R-1)/R of half that over NVLink, whatever R is. The
+// full result is in a rank's output buffer once every rank's launch has finished (a second barrier).
+template <bool kBf16>
+__global__ void __launch_bounds__(256) dbias_sum_peers_sliced_kernel(const float* const* __restrict__ parts,
+                                                                     uint16_t* const* __restrict__ outs, int nranks,
+                                                                     int rank, long long n) {
+  constexpr int U = 4;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long nvec = n / 8;
+  const long long per = (nvec + nranks - 1) / nranks;
+  const long long v_begin = rank * per, v_end = (v_begin + per < nvec) ? v_begin + per : nvec;
+  for (long long v0 = v_begin + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < v_end;
+       v0 += U * nthreads) {
+    float4 acc[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u][0] = acc[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < nranks; ++r) {
+      const float4* src = reinterpret_cast<const float4*>(parts[r]);
+      float4 x[U][2];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long v = v0 + u * nthreads;
+        if (v < v_end) {
+          x[u][0] = __ldcg(src + 2 * v);
+          x[u][1] = __ldcg(src + 2 * v + 1);
+        } else {
+          x[u][0] = x[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          acc[u][hlf].x += x[u][hlf].x;
+          acc[u][hlf].y += x[u][hlf].y;
+          acc[u][hlf].z += x[u][hlf].z;
+          acc[u][hlf].w += x[u][hlf].w;
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + u * nthreads;
+      if (v >= v_end) continue;
+      uint4 pk;
+      pk.x = pack2<kBf16>(acc[u][0].x, acc[u][0].y);
+      pk.y = pack2<kBf16>(acc[u][0].z, acc[u][0].w);
+      pk.z = pack2<kBf16>(acc[u][1].x, acc[u][1].y);
+      pk.w = pack2<kBf16>(acc[u][1].z, acc[u][1].w);
+      for (int r = 0; r < nranks; ++r) reinterpret_cast<uint4*>(outs[r])[v] = pk;
     }
   }
 }
@@ -531,10 +627,24 @@ int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaS
 }
 
 int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, float* out_f32, void* out_cast,
-                           bool bf16, cudaStream_t stream) {
+                           bool bf16, int* const* flags, int rank, int epoch, unsigned long long limit_ns, int* status,
+                           cudaStream_t stream) {
   const int grid = grid_for((n / 8 + 3) / 4, 256);
-  if (bf16) dbias_sum_peers_kernel<true><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, static_cast<uint16_t*>(out_cast));
-  else dbias_sum_peers_kernel<false><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, static_cast<uint16_t*>(out_cast));
+  uint16_t* oc = static_cast<uint16_t*>(out_cast);
+  if (bf16)
+    dbias_sum_peers_kernel<true><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, oc, flags, rank, epoch, limit_ns, status);
+  else
+    dbias_sum_peers_kernel<false><<<grid, 256, 0, stream>>>(parts, nranks, n, out_f32, oc, flags, rank, epoch, limit_ns, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int launch_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int nranks, int rank, long long n,
+                                  bool bf16, cudaStream_t stream) {
+  const long long per = (n / 8 + nranks - 1) / nranks;
+  const int grid = grid_for((per + 3) / 4, 256);
+  uint16_t* const* o = reinterpret_cast<uint16_t* const*>(outs);
+  if (bf16) dbias_sum_peers_sliced_kernel<true><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n);
+  else dbias_sum_peers_sliced_kernel<false><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n);
   return static_cast<int>(cudaGetLastError());
 }
 

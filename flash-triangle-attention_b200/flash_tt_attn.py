@@ -271,13 +271,13 @@ class PeerDbiasSum:
     Every rank of ``group`` keeps its float32 partial dBias in a buffer that the other ranks can
     address (``torch.distributed._symmetric_memory``: one allocation per rank, exchanged once at
     construction - a collective call). ``partial()`` is the tensor to hand to ``fta_backward`` as
-    ``dbias_f32``; ``reduce()`` lines the ranks up (the symmetric-memory barrier, on the current
-    stream) and launches ``fta_dbias_sum_peers``: each rank reads all partials itself, adds them in
-    rank order and rounds once - one short kernel where the all-reduce is a ~30-50 us collective
-    plus a cast. Two partial buffers are used in turn, so that a rank may write its next partial
-    while a slower peer still reads the previous one. Every rank reads (world - 1) partials, which
-    pays for small groups (the pairs of an 8-GPU heads-first split); larger groups are better off
-    with the all-reduce. Construction raises where symmetric memory is unavailable: callers fall back
+    ``dbias_f32``; ``reduce()`` is one launch of ``fta_dbias_sum_peers_sync``: the kernel lines the ranks
+    up itself (epoch words the ranks write into each other's memory, a bounded wait), then each rank
+    reads all partials, adds them in rank order and rounds once - one short kernel where the
+    all-reduce is a ~30-50 us collective plus a cast. Two partial buffers are used in turn, so that a rank may write its next partial
+    while a slower peer still reads the previous one. Every rank reading (world - 1) partials pays
+    for pairs (an 8-GPU heads-first split); larger groups use ``reduce_sliced``: each rank sums a
+    1/world slice and stores the rounded result into every rank's (symmetric) output buffer. Construction raises where symmetric memory is unavailable: callers fall back
     to ``torch.distributed.all_reduce`` + ``fta_dbias_cast``."""
 
     def __init__(self, shape, group, device, dtype):
@@ -296,6 +296,22 @@ class PeerDbiasSum:
         base = [int(p) for p in self.hdl.buffer_ptrs]
         self.parts = [torch.tensor([p + slot * self.n * 4 for p in base], dtype=torch.int64, device=device)
                       for slot in (0, 1)]
+        # epoch words for the line-up inside the kernel (fta_dbias_sum_peers_sync): one array of `world`
+        # words per rank, written by the peers; zero on every rank before anybody's first launch
+        self.flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.flags_hdl = symm_mem.rendezvous(self.flags, group)
+        self._flag_ptrs = torch.tensor([int(p) for p in self.flags_hdl.buffer_ptrs], dtype=torch.int64, device=device)
+        self.rank = int(self.hdl.rank)
+        self.status = _status_of(torch.device(device))
+        self.flags_hdl.barrier(channel=0)
+        # groups of more than two: each rank sums a slice and stores the rounded result into every
+        # rank's output buffer (fta_dbias_sum_peers_sliced), also symmetric memory
+        self.sliced = self.world > 2
+        if self.sliced:
+            self.out = symm_mem.empty((self.n,), dtype=dtype, device=device)
+            self.out_hdl = symm_mem.rendezvous(self.out, group)
+            self._outs = torch.tensor([int(p) for p in self.out_hdl.buffer_ptrs], dtype=torch.int64, device=device)
         self._views = [self.buf[slot].view(self.shape) for slot in (0, 1)]
         self._ptrs = [v.data_ptr() for v in self._views]
         self._parts_ptrs = [t.data_ptr() for t in self.parts]
@@ -309,15 +325,32 @@ class PeerDbiasSum:
     def partial_ptr(self):
         return self._ptrs[self.step & 1]
 
-    def reduce(self, out_cast, out_f32=None, stream=None):
-        """After this rank's ``fta_backward`` has been enqueued: barrier, sum over the ranks, round."""
+    def reduce(self, out_cast, out_f32=None, stream=None, wait_limit_ns=0):
+        """After this rank's ``fta_backward`` has been enqueued: ONE launch that lines the ranks up (epoch
+        words in peer memory, bounded wait: a peer that never arrives leaves a code in the status word
+        instead of a hang), sums the partials in rank order and rounds."""
+        stream = torch.cuda.current_stream(self.buf.device).cuda_stream if stream is None else stream
+        check(self._lib.fta_dbias_sum_peers_sync(self._parts_ptrs[self.step & 1], self._flag_ptrs.data_ptr(), self.world,
+                                                 self.rank, self.step + 1, self.n,
+                                                 None if out_f32 is None else out_f32.data_ptr(),
+                                                 None if out_cast is None else out_cast.data_ptr(), self.dtype_code,
+                                                 int(wait_limit_ns), self.status.word.data_ptr(), stream),
+              "fta_dbias_sum_peers_sync")
+        self.step += 1
+
+    def reduce_sliced(self, stream=None):
+        """Groups of more than two ranks: barrier, every rank sums its slice and stores the rounded result
+        into every rank's output buffer, barrier. Returns this rank's output buffer (shape of the
+        partial, bias dtype): valid until the next ``reduce_sliced``."""
+        assert self.sliced
         stream = torch.cuda.current_stream(self.buf.device).cuda_stream if stream is None else stream
         self.hdl.barrier(channel=0)
-        check(self._lib.fta_dbias_sum_peers(self._parts_ptrs[self.step & 1], self.world, self.n,
-                                            None if out_f32 is None else out_f32.data_ptr(),
-                                            None if out_cast is None else out_cast.data_ptr(), self.dtype_code,
-                                            stream), "fta_dbias_sum_peers")
+        check(self._lib.fta_dbias_sum_peers_sliced(self._parts_ptrs[self.step & 1], self._outs.data_ptr(), self.world,
+                                                   self.rank, self.n, self.dtype_code, stream),
+              "fta_dbias_sum_peers_sliced")
+        self.hdl.barrier(channel=0)
         self.step += 1
+        return self.out.view(self.shape)
 
 
 def _block_sizes(L1: int, block_rows: int):

@@ -174,6 +174,32 @@ FTA_API int fta_dbias_cast(const float* src, void* dst, int64_t n, int32_t dtype
 FTA_API int fta_dbias_sum_peers(const float* const* parts, int32_t nranks, int64_t n, float* out_f32,
                         void* out_cast, int32_t dtype, void* stream);
 
+/* fta_dbias_sum_peers with the line-up of the ranks inside the kernel, so that the sum is ONE launch
+ * per rank and step with no barrier launch and no library collective. `flags`: device array of
+ * `nranks` device pointers, entry r = rank r's array of `nranks` int32 epoch words as this GPU sees it
+ * (zero before the first call, in memory every rank can write: the same kind of peer mapping as the
+ * partials). `epoch` = 1, 2, 3, ... the same on every rank for the same step. The kernel publishes
+ * "rank `rank`'s partial of this epoch is complete" (it was written by earlier work on `stream`) into
+ * every rank's words, waits until all `nranks` words of this rank have reached `epoch`, then sums.
+ * The wait is bounded: after `wait_limit_ns` (0 = one second) of the GPU's global timer the kernel
+ * writes 0x1000 | 0x61 to `status` and returns without output - nothing traps, the context stays
+ * usable. Partials must alternate between two buffers from step to step (a rank may be one step ahead
+ * of a peer that is still reading). One process per GPU: never two ranks as kernels on one GPU.
+ * No counterpart in the reference. */
+FTA_API int fta_dbias_sum_peers_sync(const float* const* parts, int32_t* const* flags, int32_t nranks,
+                             int32_t rank, int32_t epoch, int64_t n, float* out_f32, void* out_cast,
+                             int32_t dtype, uint64_t wait_limit_ns, int32_t* status, void* stream);
+
+/* The same sum with the work split over the ranks (reduce-scatter and all-gather in one kernel), for
+ * groups where every rank reading every partial would be too much traffic: rank `rank` adds the
+ * partials of its 1/nranks slice of the elements (rank order), rounds, and stores the 16-bit result
+ * into EVERY rank's output buffer. `outs`: device array of `nranks` device pointers to the ranks'
+ * (n-element, 16-bit, 16-byte aligned) output buffers as this GPU sees them. The caller lines the ranks
+ * up before the launch (partials complete, previous outputs consumed) and once more after it: a rank's
+ * output buffer is complete when every rank's launch has finished. No counterpart in the reference. */
+FTA_API int fta_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int32_t nranks,
+                               int32_t rank, int64_t n, int32_t dtype, void* stream);
+
 /* Backward pass without a caller-provided workspace. It has no counterpart in the reference.
  * For callers that cannot allocate device memory where they call this library (a framework's
  * memory-planning phase, a plugin interface that only passes inputs and outputs, a loop that

@@ -108,3 +108,34 @@ def test_one_process_two_devices():
         outs.append([o.detach().cpu(), t["q"].grad.cpu(), t["k"].grad.cpu(), t["v"].grad.cpu(), t["bias"].grad.cpu()])
     for a, b_ in zip(*outs[:2]):
         assert torch.equal(a, b_) or np.allclose(a.float().numpy(), b_.float().numpy(), atol=2e-2)
+
+
+def test_peer_sum_wait_runs_out_without_a_peer():
+    """fta_dbias_sum_peers_sync waits for every rank's epoch word; here "rank 1" is a second buffer on the
+    same GPU whose word nobody ever writes, so the 5 ms wait runs out: the kernel must leave
+    0x1000 | 0x61 in the status word, write no output, return, and the device must stay usable."""
+    import _cabi
+    L = _cabi.lib()
+    dev = torch.device("cuda", 0)
+    n = 4096
+    parts = [torch.ones(n, device=dev), torch.ones(n, device=dev)]
+    flags = [torch.zeros(2, dtype=torch.int32, device=dev), torch.zeros(2, dtype=torch.int32, device=dev)]
+    pp = torch.tensor([p.data_ptr() for p in parts], dtype=torch.int64, device=dev)
+    fp = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.full((n,), -7.0, dtype=torch.bfloat16, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    rc = L.fta_dbias_sum_peers_sync(pp.data_ptr(), fp.data_ptr(), 2, 0, 1, n, None, out.data_ptr(), _cabi.FTA_BF16,
+                                    5_000_000, status.data_ptr(), st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == (0x1000 | 0x61)
+    assert bool((out == -7.0).all())           # no output after a failed line-up
+    assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1   # this rank did publish its epoch everywhere
+    # the word of "rank 1" set by hand: the same call now goes through
+    status.zero_()
+    flags[0][1] = 1
+    rc = L.fta_dbias_sum_peers_sync(pp.data_ptr(), fp.data_ptr(), 2, 0, 1, n, None, out.data_ptr(), _cabi.FTA_BF16,
+                                    5_000_000, status.data_ptr(), st)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 0 and bool((out == 2.0).all())

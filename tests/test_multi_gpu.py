@@ -84,6 +84,21 @@ for step in range(5):   # both partial buffers, several times over
     both = [torch.empty_like(out32) for _ in range(world)]
     dist.all_gather(both, out32)
     assert torch.equal(both[0], both[1])
+# the sliced variant (what groups of more than two use), forced on for this pair
+import torch.distributed._symmetric_memory as symm_mem
+out_sym = symm_mem.empty((peer.n,), dtype=torch.bfloat16, device=dev)
+oh = symm_mem.rendezvous(out_sym, dist.group.WORLD)
+outs = torch.tensor([int(p) for p in oh.buffer_ptrs], dtype=torch.int64, device=dev)
+for step in range(3):
+    g = torch.Generator(device=dev).manual_seed(777 * step + rank)
+    part = torch.randn(B, H, L2, L2, device=dev, generator=g) * 3.0
+    peer.partial().copy_(part)
+    peer.hdl.barrier(channel=0)
+    assert L.fta_dbias_sum_peers_sliced(peer.parts[peer.step & 1].data_ptr(), outs.data_ptr(), world, rank, peer.n, 1, stream) == 0
+    peer.hdl.barrier(channel=0)
+    peer.step += 1
+    ref = part.clone(); dist.all_reduce(ref); torch.cuda.synchronize()
+    assert torch.equal(out_sym.view(B, H, L2, L2), ref.to(torch.bfloat16)), step
 # argument checks of the entry point, no launch
 assert L.fta_dbias_sum_peers(None, 2, 64, None, out16.data_ptr(), 1, stream) == -1
 assert L.fta_dbias_sum_peers(peer.parts[0].data_ptr(), 2, 60, None, out16.data_ptr(), 1, stream) == -2
