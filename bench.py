@@ -92,7 +92,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.first = index, [], None, 0
 
     def start(self):
         try:
@@ -107,15 +107,26 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def wait_first_sample(self, timeout_s=3.0):
+        """nvidia-smi takes a good part of a second to initialise (and perturbs launches while it does):
+        callers start it ahead of the warm-up and begin timing once it delivers samples."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.rows and time.perf_counter() - t0 < timeout_s:
+            time.sleep(0.02)
+
+    def mark_region_start(self):
+        self.first = len(self.rows)
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
-        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        rows = self.rows[self.first:] or self.rows  # samples taken from the start of the timed region on
+        sm = [float(r[1]) for r in rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v == "Active"})
+        reasons = sorted({n for r in rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v == "Active"})
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -447,15 +458,19 @@ def main():
                 _cabi.check(L.fta_dbias_cast(p_db32, p_db, n_db, prob.dtype, stream), "fta_dbias_cast")
                 mark("cast")
 
+        # the clock sampler starts before the warm-up: its start-up is over when the timed region begins
+        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
+        if sampler:
+            sampler.start()
+            sampler.wait_first_sample()
         for _ in range(warmup):
             step()
         barrier()
         # ---- timed region: K steps, each bracketed by CUDA events on the launching stream; L2 is
         # flushed (a 256 MB write) between steps, outside the events. The host only enqueues: events
         # are read after the loop, so the GPU always has the next launches queued.
-        sampler = ClockSampler(local) if (sample_clocks and rank == 0) else None
         if sampler:
-            sampler.start()
+            sampler.mark_region_start()
         barrier()
         wall0 = time.perf_counter()
         evs = []
