@@ -561,22 +561,25 @@ def main():
             # copies in / kernels / copies out on three streams
             fta.attention_fwd_bwd_streamed(host, scale, out_host, block_rows=E2E_BLOCK_ROWS, device=dev, group=grp)
 
-        for _ in range(3):  # untimed: first touches of the pinned buffers, allocator, streams
-            e2e_step()
-        barrier()
-        e2e_ms = []
-        for _ in range(e2e_steps):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            e2e_step()
-            e1.record()
-            torch.cuda.synchronize()
-            e2e_ms.append(e0.elapsed_time(e1))
-        barrier()
-        te = torch.tensor([float(np.sum(e2e_ms))], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ms_step = float(te.item()) / e2e_steps
+        def measure_e2e():
+            for _ in range(3):  # untimed: first touches of the pinned buffers, allocator, streams
+                e2e_step()
+            barrier()
+            ms = []
+            for _ in range(e2e_steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                e2e_step()
+                e1.record()
+                torch.cuda.synchronize()
+                ms.append(e0.elapsed_time(e1))
+            barrier()
+            te = torch.tensor([float(np.sum(ms))], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            return ms, float(te.item()) / e2e_steps
+
+        e2e_ms, e2e_ms_step = measure_e2e()
         # the bound of this leg: the same pinned buffers copied in and out at the same time with
         # nothing else going on (two streams, whole tensors)
         dbuf = {k: torch.empty_like(v, device=dev) for k, v in host.items()}
@@ -607,10 +610,21 @@ def main():
             return best
 
         t_in, t_out, t_both = copy_ms(True, False), copy_ms(False, True), copy_ms(True, True)
+        # The host side of this leg (a shared machine: PCIe root, driver locks, host cores) now and then
+        # runs whole calls at 70-100 ms where 15 ms is normal, with the copy bound measured right after
+        # at its usual value. A leg that far off its own bound is taken once more and both are reported.
+        e2e_first = None
+        flag = torch.tensor([1.0 if e2e_ms_step > 2.5 * t_both else 0.0], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if float(flag.item()) > 0:
+            e2e_first = e2e_ms_step
+            e2e_ms, e2e_ms_step = measure_e2e()
         e2e = {"value": flops_step / (e2e_ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "steps": e2e_steps, "ms_per_step": e2e_ms_step,
                # this rank's median beside the mean: the host link is shared, single steps of 25-28 ms occur
                "ms_per_step_median": float(np.median(e2e_ms)),
+               "first_attempt_ms_per_step": e2e_first,  # not None: the leg was re-measured once (see bench.py)
                "h2d_only_gbs": h2d / t_in / 1e6, "d2h_only_gbs": d2h / t_out / 1e6,
                "copy_bound_ms": t_both, "frac_of_copy_bound": t_both / e2e_ms_step,
                "note": "per rank: its shard of q,k,v,dO + bias in, o,dq,dk,dv + dbias out; copy_bound_ms = the same "

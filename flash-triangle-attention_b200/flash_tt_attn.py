@@ -42,6 +42,7 @@ __all__ = ["attention", "attention_fwd_bwd_streamed", "reference_tt_attn", "chec
 _DEBUG = os.environ.get("FTA_DEBUG", "0") == "1"
 _SAVE_O_RESIDUAL = os.environ.get("FTA_SAVE_O_RESIDUAL", "1") != "0"
 _status_words = {}
+_copy_streams = {}
 _last = {"dbias_f32": None}
 
 
@@ -412,7 +413,12 @@ def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, 
         cur = torch.cuda.current_stream(dev)
         st = _status_of(dev)
         st.raise_if_set()
-        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        # the two copy streams are kept per device: every new side stream has its own allocator pool,
+        # and a tensor allocated under it costs a cudaMalloc per call until the pools have filled up
+        key = (dev.type, dev.index)
+        if key not in _copy_streams:
+            _copy_streams[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+        s_in, s_out = _copy_streams[key]
         sizes = _block_sizes(L1, block_rows)
         cap = max(sizes)
         mk = lambda *shape, dtype=q_h.dtype: torch.empty(shape, dtype=dtype, device=dev)
@@ -424,9 +430,10 @@ def attention_fwd_bwd_streamed(host, sm_scale, out, block_rows=96, device=None, 
         ev_in = [torch.cuda.Event() for _ in range(NSLOT)]
         ev_comp = [torch.cuda.Event() for _ in range(NSLOT)]
         ev_out = [torch.cuda.Event() for _ in range(NSLOT)]
+        bias = torch.empty(b_h.shape, dtype=b_h.dtype, device=dev)  # from the current stream's pool
         s_in.wait_stream(cur)
         with torch.cuda.stream(s_in):
-            bias = b_h.to(dev, non_blocking=True)
+            bias.copy_(b_h, non_blocking=True)
         cur.wait_stream(s_in)
         bias_k = bias
         if L2p != L2:
