@@ -532,7 +532,7 @@ def main():
                 "wall_ms_per_step_incl_flush": wall / steps * 1e3, "heads_per_gpu": H, "rows_per_gpu": nrows,
                 "allreduce_ranks": 1 if grp is None else dist.get_world_size(grp),
                 "launches_per_step": 5 + (1 if sharded else 0),  # fwd, preprocess, bwd prologue / kernel / epilogue (+ cast or peer sum)
-                "dbias_sum": "none" if not sharded else (("peer memory (fta_dbias_sum_peers_sliced)" if peer.sliced else "peer memory (fta_dbias_sum_peers_sync: one launch)") if peer else "nccl all-reduce + cast"),
+                "dbias_sum": "none" if not sharded else (("peer memory (fta_dbias_sum_peers_sliced_sync)" if peer.sliced else "peer memory (fta_dbias_sum_peers_sync: one launch)") if peer else "nccl all-reduce + cast"),
                 "launch_ms": launch_ms,
                 "host": host, "grp": grp}
 

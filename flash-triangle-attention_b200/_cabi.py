@@ -38,7 +38,7 @@ _lib = None
 # every symbol include/fta.h declares
 EXPORTS = (
     "fta_version", "fta_strerror", "fta_last_cuda_error", "fta_forward", "fta_bwd_preprocess",
-    "fta_bwd_workspace_bytes", "fta_bwd_num_planes", "fta_backward", "fta_dbias_cast", "fta_dbias_sum_peers", "fta_dbias_sum_peers_sync", "fta_dbias_sum_peers_sliced",
+    "fta_bwd_workspace_bytes", "fta_bwd_num_planes", "fta_backward", "fta_dbias_cast", "fta_dbias_sum_peers", "fta_dbias_sum_peers_sync", "fta_dbias_sum_peers_sliced", "fta_dbias_sum_peers_sliced_sync",
     "fta_read_status", "fta_profile_backward_kernel", "fta_backward_noalloc", "fta_noalloc_max_bytes",
     "fta_memcpy_2d", "fta_mask_bias",
 )
@@ -77,6 +77,9 @@ def lib():
     L.fta_dbias_sum_peers_sync.restype = ctypes.c_int
     L.fta_dbias_sum_peers_sync.argtypes = [vp, vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, vp, vp,
                                            ctypes.c_int32, ctypes.c_uint64, vp, vp]
+    L.fta_dbias_sum_peers_sliced_sync.restype = ctypes.c_int
+    L.fta_dbias_sum_peers_sliced_sync.argtypes = [vp, vp, vp, vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
+                                                  ctypes.c_int32, ctypes.c_uint64, vp, vp]
     L.fta_dbias_sum_peers_sliced.restype = ctypes.c_int
     L.fta_dbias_sum_peers_sliced.argtypes = [vp, vp, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp]
     L.fta_read_status.restype = ctypes.c_int

@@ -328,8 +328,24 @@ int fta_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int
   if (nranks < 1 || nranks > 64 || rank < 0 || rank >= nranks || n <= 0 || n % 8 != 0) return FTA_ERR_SHAPE;
   if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
   if ((reinterpret_cast<uintptr_t>(parts) & 7u) || (reinterpret_cast<uintptr_t>(outs) & 7u)) return FTA_ERR_ALIGN;
-  if (const int e = fta::launch_dbias_sum_peers_sliced(parts, outs, nranks, rank, n, dtype == FTA_BF16,
-                                                       static_cast<cudaStream_t>(stream)))
+  if (const int e = fta::launch_dbias_sum_peers_sliced(parts, outs, nranks, rank, n, dtype == FTA_BF16, nullptr, nullptr, 0,
+                                                       0, nullptr, static_cast<cudaStream_t>(stream)))
+    return cuda_fail(e);
+  return FTA_OK;
+}
+
+int fta_dbias_sum_peers_sliced_sync(const float* const* parts, void* const* outs, int32_t* const* flags,
+                                    const int32_t* my_flags, int32_t nranks, int32_t rank, int32_t epoch, int64_t n,
+                                    int32_t dtype, uint64_t wait_limit_ns, int32_t* status, void* stream) {
+  if (!parts || !outs || !flags || !my_flags || !status) return FTA_ERR_NULL;
+  if (nranks < 1 || nranks > 31 || rank < 0 || rank >= nranks || epoch <= 0 || n <= 0 || n % 8 != 0) return FTA_ERR_SHAPE;
+  if (dtype != FTA_FP16 && dtype != FTA_BF16) return FTA_ERR_DTYPE;
+  if ((reinterpret_cast<uintptr_t>(parts) & 7u) || (reinterpret_cast<uintptr_t>(outs) & 7u) ||
+      (reinterpret_cast<uintptr_t>(flags) & 7u) || (reinterpret_cast<uintptr_t>(my_flags) & 3u))
+    return FTA_ERR_ALIGN;
+  if (wait_limit_ns == 0) wait_limit_ns = 1000000000ull;
+  if (const int e = fta::launch_dbias_sum_peers_sliced(parts, outs, nranks, rank, n, dtype == FTA_BF16, flags, my_flags, epoch,
+                                                       wait_limit_ns, status, static_cast<cudaStream_t>(stream)))
     return cuda_fail(e);
   return FTA_OK;
 }

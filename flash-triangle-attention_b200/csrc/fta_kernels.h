@@ -100,8 +100,12 @@ int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, f
                            cudaStream_t stream);
 // the same with the work split over the ranks: this rank sums its 1/nranks slice and stores the rounded
 // result into every rank's buffer `outs[r]` (device array of nranks device pointers)
+// `flags` == nullptr: the caller lines the ranks up before and after; otherwise the kernel does, and a
+// one-block kernel behind it holds the stream until every rank's slice has arrived (`my_flags`: this
+// rank's own flag array, 2 * nranks + 1 words)
 int launch_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int nranks, int rank, long long n,
-                                  bool bf16, cudaStream_t stream);
+                                  bool bf16, int* const* flags, const int* my_flags, int epoch,
+                                  unsigned long long limit_ns, int* status, cudaStream_t stream);
 // dst[i] = (dtype) src[i], n a multiple of 4
 int launch_dbias_cast(const float* src, long long n, void* dst, bool bf16, cudaStream_t stream);
 

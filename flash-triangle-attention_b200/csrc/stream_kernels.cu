@@ -242,10 +242,39 @@ __global__ void __launch_bounds__(256) dbias_sum_peers_kernel(const float* const
 // every rank's output buffer (`outs`: device array of R pointers, peer mappings included). Each rank
 // then reads (R-1)/R of one partial and writes (R-1)/R of half that over NVLink, whatever R is. The
 // full result is in a rank's output buffer once every rank's launch has finished (a second barrier).
+// With `flags` the kernel lines the ranks up itself, like dbias_sum_peers_kernel (words [0, R) of a rank's
+// flag array: "rank r's partial of this epoch is complete"), and when its last block has stored its last
+// vector it publishes "rank `rank`'s slice is in your output buffer" into word R + rank of every
+// rank's array (the blocks count themselves out on word 2R of this rank's own array).
+// peers_wait_kernel, launched behind it, then holds the stream until all R slices have arrived.
 template <bool kBf16>
 __global__ void __launch_bounds__(256) dbias_sum_peers_sliced_kernel(const float* const* __restrict__ parts,
                                                                      uint16_t* const* __restrict__ outs, int nranks,
-                                                                     int rank, long long n) {
+                                                                     int rank, long long n, int* const* flags, int epoch,
+                                                                     unsigned long long limit_ns, int* status) {
+  __shared__ int s_last;
+  if (flags != nullptr) {
+    if (blockIdx.x == 0 && static_cast<int>(threadIdx.x) < nranks) {
+      __threadfence_system();
+      st_release_sys_u32(flags[threadIdx.x] + rank, epoch);
+    }
+    bool ok = true;
+    if (static_cast<int>(threadIdx.x) < nranks) {
+      const int* mine = flags[rank] + threadIdx.x;
+      const unsigned long long t0 = global_timer_ns();
+      while (ld_acquire_sys_u32(mine) - epoch < 0) {
+        if (global_timer_ns() - t0 > limit_ns) {
+          ok = false;
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+    if (!__syncthreads_and(ok)) {
+      if (threadIdx.x == 0) atomicCAS(status, kStatusOk, kStatusWaitTimeout | 0x62);
+      return;
+    }
+  }
   constexpr int U = 4;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long nvec = n / 8;
@@ -291,6 +320,39 @@ __global__ void __launch_bounds__(256) dbias_sum_peers_sliced_kernel(const float
       for (int r = 0; r < nranks; ++r) reinterpret_cast<uint4*>(outs[r])[v] = pk;
     }
   }
+  if (flags != nullptr) {
+    __threadfence_system();  // this thread's stores into the peers' buffers are visible system-wide
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int* counter = flags[rank] + 2 * nranks;
+      const int done = atomicAdd(counter, 1);
+      s_last = (done == static_cast<int>(gridDim.x) - 1);
+      if (s_last) *counter = 0;  // for the next launch (launches of one rank are stream-ordered)
+    }
+    __syncthreads();
+    if (s_last && static_cast<int>(threadIdx.x) < nranks) {
+      __threadfence_system();
+      st_release_sys_u32(flags[threadIdx.x] + nranks + rank, epoch);
+    }
+  }
+}
+
+// Holds the stream until words [R, 2R) of this rank's flag array have reached `epoch`: every rank's slice
+// of the sum is then in this rank's output buffer. One block; bounded like every other wait here.
+__global__ void __launch_bounds__(64) peers_wait_kernel(const int* done_words, int nranks, int epoch,
+                                                        unsigned long long limit_ns, int* status) {
+  bool ok = true;
+  if (static_cast<int>(threadIdx.x) < nranks) {
+    const unsigned long long t0 = global_timer_ns();
+    while (ld_acquire_sys_u32(done_words + threadIdx.x) - epoch < 0) {
+      if (global_timer_ns() - t0 > limit_ns) {
+        ok = false;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  if (!__syncthreads_and(ok) && threadIdx.x == 0) atomicCAS(status, kStatusOk, kStatusWaitTimeout | 0x63);
 }
 
 // Padded, masked copy of the pair bias for problems whose L2 is not a multiple of 128 and / or that
@@ -639,13 +701,21 @@ int launch_dbias_sum_peers(const float* const* parts, int nranks, long long n, f
 }
 
 int launch_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int nranks, int rank, long long n,
-                                  bool bf16, cudaStream_t stream) {
+                                  bool bf16, int* const* flags, const int* my_flags, int epoch,
+                                  unsigned long long limit_ns, int* status, cudaStream_t stream) {
   const long long per = (n / 8 + nranks - 1) / nranks;
   const int grid = grid_for((per + 3) / 4, 256);
   uint16_t* const* o = reinterpret_cast<uint16_t* const*>(outs);
-  if (bf16) dbias_sum_peers_sliced_kernel<true><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n);
-  else dbias_sum_peers_sliced_kernel<false><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n);
-  return static_cast<int>(cudaGetLastError());
+  if (bf16)
+    dbias_sum_peers_sliced_kernel<true><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n, flags, epoch, limit_ns, status);
+  else
+    dbias_sum_peers_sliced_kernel<false><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n, flags, epoch, limit_ns, status);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && flags != nullptr) {
+    peers_wait_kernel<<<1, 64, 0, stream>>>(my_flags + nranks, nranks, epoch, limit_ns, status);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
 }
 
 }  // namespace fta

@@ -339,17 +339,19 @@ class PeerDbiasSum:
               "fta_dbias_sum_peers_sync")
         self.step += 1
 
-    def reduce_sliced(self, stream=None):
-        """Groups of more than two ranks: barrier, every rank sums its slice and stores the rounded result
-        into every rank's output buffer, barrier. Returns this rank's output buffer (shape of the
-        partial, bias dtype): valid until the next ``reduce_sliced``."""
+    def reduce_sliced(self, stream=None, wait_limit_ns=0):
+        """Groups of more than two ranks: every rank sums its 1/world slice and stores the rounded result
+        into every rank's output buffer; the line-ups before (partials complete) and after (all slices
+        arrived) happen inside the two kernels ``fta_dbias_sum_peers_sliced_sync`` enqueues, with bounded
+        waits. Returns this rank's output buffer (shape of the partial, bias dtype): complete for work
+        enqueued on the same stream after this call, valid until the next ``reduce_sliced``."""
         assert self.sliced
         stream = torch.cuda.current_stream(self.buf.device).cuda_stream if stream is None else stream
-        self.hdl.barrier(channel=0)
-        check(self._lib.fta_dbias_sum_peers_sliced(self._parts_ptrs[self.step & 1], self._outs.data_ptr(), self.world,
-                                                   self.rank, self.n, self.dtype_code, stream),
-              "fta_dbias_sum_peers_sliced")
-        self.hdl.barrier(channel=0)
+        check(self._lib.fta_dbias_sum_peers_sliced_sync(self._parts_ptrs[self.step & 1], self._outs.data_ptr(),
+                                                        self._flag_ptrs.data_ptr(), self.flags.data_ptr(), self.world,
+                                                        self.rank, self.step + 1, self.n, self.dtype_code,
+                                                        int(wait_limit_ns), self.status.word.data_ptr(), stream),
+              "fta_dbias_sum_peers_sliced_sync")
         self.step += 1
         return self.out.view(self.shape)
 

@@ -200,6 +200,20 @@ FTA_API int fta_dbias_sum_peers_sync(const float* const* parts, int32_t* const* 
 FTA_API int fta_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, int32_t nranks,
                                int32_t rank, int64_t n, int32_t dtype, void* stream);
 
+/* fta_dbias_sum_peers_sliced with both line-ups inside: the ranks wait for each other's partials in the
+ * kernel (as in fta_dbias_sum_peers_sync; words [0, nranks) of a rank's flag array), each rank
+ * publishes "my slice is in your buffer" when its last block is done (words [nranks, 2 nranks); word
+ * 2 nranks of a rank's OWN array is the block counter), and a one-block kernel enqueued behind the sum
+ * holds `stream` until all slices have arrived: work enqueued after this call sees the complete result
+ * in this rank's output buffer. `flags`: device array of the ranks' flag arrays (2 nranks + 1 int32
+ * each, zero before the first call) as this GPU sees them; `my_flags`: this rank's own array (local
+ * address). Same epoch rule, same bounded waits (status 0x1000 | 0x62 / 0x63), nranks <= 31.
+ * No counterpart in the reference. */
+FTA_API int fta_dbias_sum_peers_sliced_sync(const float* const* parts, void* const* outs, int32_t* const* flags,
+                                    const int32_t* my_flags, int32_t nranks, int32_t rank, int32_t epoch,
+                                    int64_t n, int32_t dtype, uint64_t wait_limit_ns, int32_t* status,
+                                    void* stream);
+
 /* Backward pass without a caller-provided workspace. It has no counterpart in the reference.
  * For callers that cannot allocate device memory where they call this library (a framework's
  * memory-planning phase, a plugin interface that only passes inputs and outputs, a loop that

@@ -99,6 +99,22 @@ for step in range(3):
     peer.step += 1
     ref = part.clone(); dist.all_reduce(ref); torch.cuda.synchronize()
     assert torch.equal(out_sym.view(B, H, L2, L2), ref.to(torch.bfloat16)), step
+# ... and with both line-ups inside the kernels (epoch words continue where reduce() left them)
+for step in range(3):
+    g = torch.Generator(device=dev).manual_seed(555 * step + rank)
+    part = torch.randn(B, H, L2, L2, device=dev, generator=g) * 3.0
+    peer.partial().copy_(part)
+    out_sym.zero_()
+    rc = L.fta_dbias_sum_peers_sliced_sync(peer.parts[peer.step & 1].data_ptr(), outs.data_ptr(), peer._flag_ptrs.data_ptr(),
+                                           peer.flags.data_ptr(), world, rank, peer.step + 1, peer.n, 1, 0,
+                                           peer.status.word.data_ptr(), stream)
+    assert rc == 0
+    peer.step += 1
+    got = out_sym.view(B, H, L2, L2).clone()      # enqueued behind the wait kernel: complete
+    ref = part.clone(); dist.all_reduce(ref); torch.cuda.synchronize()
+    fta.check_device_status()
+    assert torch.equal(got, ref.to(torch.bfloat16)), step
+    dist.barrier()   # nobody zeroes its buffer while the other rank still writes into it
 # argument checks of the entry point, no launch
 assert L.fta_dbias_sum_peers(None, 2, 64, None, out16.data_ptr(), 1, stream) == -1
 assert L.fta_dbias_sum_peers(peer.parts[0].data_ptr(), 2, 60, None, out16.data_ptr(), 1, stream) == -2
