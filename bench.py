@@ -312,7 +312,7 @@ def main():
                     help="multi-GPU partition of the headline value (the other one is reported beside it)")
     ap.add_argument("--dbias-sum", default="auto", choices=["auto", "nccl", "peer"],
                     help="ranks that share a head sum dBias with an NCCL all-reduce + cast, or with "
-                         "fta_dbias_sum_peers_sync / _sliced over NVLink peer memory (auto: peer memory for pairs)")
+                         "fta_dbias_sum_peers_sync / _sliced over NVLink peer memory (auto: peer memory where symmetric memory works)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-triton", action="store_true", help="skip the reference-Triton comparison table")
@@ -404,12 +404,13 @@ def main():
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         sharded = grp is not None
-        # how the ranks of a group sum dBias. auto: a pair over NVLink peer memory (one launch per rank:
-        # line-up, the other rank's partial read, sum, rounding), larger groups with an NCCL all-reduce +
-        # cast (measured at 8 ranks: 0.097 ms against 0.118 for the sliced peer-memory kernel between two
-        # barriers). --dbias-sum peer / nccl force one or the other.
+        # how the ranks of a group sum dBias. auto / peer: over NVLink peer memory - a pair with one launch
+        # per rank (line-up, the other rank's partial read, sum, rounding), larger groups with the sliced
+        # kernel (each rank sums 1/R and stores the result into every rank's buffer; 8 ranks: 0.080 ms
+        # against 0.097 for NCCL all-reduce + cast, 4 ranks: equal). nccl: the library collective, also the
+        # fallback where symmetric memory is unavailable.
         peer = None
-        if sharded and (args.dbias_sum == "peer" or (args.dbias_sum == "auto" and dist.get_world_size(grp) == 2)):
+        if sharded and args.dbias_sum in ("peer", "auto"):
             try:
                 peer = fta.PeerDbiasSum(db32.shape, grp, dev, dt)
             except Exception as e:  # symmetric memory unavailable: the all-reduce does it

@@ -275,50 +275,40 @@ __global__ void __launch_bounds__(256) dbias_sum_peers_sliced_kernel(const float
       return;
     }
   }
-  constexpr int U = 4;
+  // One 8-element vector per thread and pass; the loads of up to eight ranks are issued together
+  // (a peer load is a round trip of a few microseconds: one round trip per eight ranks, not one per
+  // rank), then added in rank order.
+  constexpr int RB = 8;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long nvec = n / 8;
   const long long per = (nvec + nranks - 1) / nranks;
   const long long v_begin = rank * per, v_end = (v_begin + per < nvec) ? v_begin + per : nvec;
-  for (long long v0 = v_begin + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v0 < v_end;
-       v0 += U * nthreads) {
-    float4 acc[U][2];
+  for (long long v = v_begin + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < v_end; v += nthreads) {
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
+    for (int r0 = 0; r0 < nranks; r0 += RB) {
+      float4 x[RB][2];
 #pragma unroll
-    for (int u = 0; u < U; ++u) acc[u][0] = acc[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < nranks; ++r) {
-      const float4* src = reinterpret_cast<const float4*>(parts[r]);
-      float4 x[U][2];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long v = v0 + u * nthreads;
-        if (v < v_end) {
-          x[u][0] = __ldcg(src + 2 * v);
-          x[u][1] = __ldcg(src + 2 * v + 1);
+      for (int k = 0; k < RB; ++k) {
+        if (r0 + k < nranks) {
+          const float4* src = reinterpret_cast<const float4*>(parts[r0 + k]) + 2 * v;
+          x[k][0] = __ldcg(src);
+          x[k][1] = __ldcg(src + 1);
         } else {
-          x[u][0] = x[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          x[k][0] = x[k][1] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf) {
-          acc[u][hlf].x += x[u][hlf].x;
-          acc[u][hlf].y += x[u][hlf].y;
-          acc[u][hlf].z += x[u][hlf].z;
-          acc[u][hlf].w += x[u][hlf].w;
-        }
+      for (int k = 0; k < RB; ++k) {
+        acc0.x += x[k][0].x; acc0.y += x[k][0].y; acc0.z += x[k][0].z; acc0.w += x[k][0].w;
+        acc1.x += x[k][1].x; acc1.y += x[k][1].y; acc1.z += x[k][1].z; acc1.w += x[k][1].w;
+      }
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long v = v0 + u * nthreads;
-      if (v >= v_end) continue;
-      uint4 pk;
-      pk.x = pack2<kBf16>(acc[u][0].x, acc[u][0].y);
-      pk.y = pack2<kBf16>(acc[u][0].z, acc[u][0].w);
-      pk.z = pack2<kBf16>(acc[u][1].x, acc[u][1].y);
-      pk.w = pack2<kBf16>(acc[u][1].z, acc[u][1].w);
-      for (int r = 0; r < nranks; ++r) reinterpret_cast<uint4*>(outs[r])[v] = pk;
-    }
+    uint4 pk;
+    pk.x = pack2<kBf16>(acc0.x, acc0.y);
+    pk.y = pack2<kBf16>(acc0.z, acc0.w);
+    pk.z = pack2<kBf16>(acc1.x, acc1.y);
+    pk.w = pack2<kBf16>(acc1.z, acc1.w);
+    for (int r = 0; r < nranks; ++r) reinterpret_cast<uint4*>(outs[r])[v] = pk;
   }
   if (flags != nullptr) {
     __threadfence_system();  // this thread's stores into the peers' buffers are visible system-wide
@@ -704,7 +694,7 @@ int launch_dbias_sum_peers_sliced(const float* const* parts, void* const* outs, 
                                   bool bf16, int* const* flags, const int* my_flags, int epoch,
                                   unsigned long long limit_ns, int* status, cudaStream_t stream) {
   const long long per = (n / 8 + nranks - 1) / nranks;
-  const int grid = grid_for((per + 3) / 4, 256);
+  const int grid = grid_for(per, 256);
   uint16_t* const* o = reinterpret_cast<uint16_t* const*>(outs);
   if (bf16)
     dbias_sum_peers_sliced_kernel<true><<<grid, 256, 0, stream>>>(parts, o, nranks, rank, n, flags, epoch, limit_ns, status);
